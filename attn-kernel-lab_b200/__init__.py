@@ -1,0 +1,26 @@
+"""B200-native (sm_100a) fused FP8 paged EXTEND/prefill attention.
+
+Same consumer-facing names as the reference package (src/attn_kernel_lab/__init__.py):
+the declared capability surface, the typed error that separates "outside the surface" from
+a defect, and the operator entry points.  The directory name is not a Python identifier, so
+import it through `__graft_entry__.package()` (or `importlib`) as `attn_kernel_lab_b200`.
+"""
+from .capability import (
+    CapabilityError,
+    GENERALIZATION_CAPABILITY,
+    OperatorCapability,
+    V1_CAPABILITY,
+    check_supported,
+)
+from .kernel import NativeError, build, load, source_build_id
+from .ops import PrefillRequest, check_request, plan_workspace, prefill_extend, prefill_extend_batch
+from .quant import CapacityPlan, FP8PrefillWorkspace, WorkspaceCapacityError
+
+__all__ = [
+    "CapabilityError", "GENERALIZATION_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
+    "check_supported", "NativeError", "build", "load", "source_build_id", "PrefillRequest",
+    "check_request", "plan_workspace", "prefill_extend", "prefill_extend_batch", "CapacityPlan",
+    "FP8PrefillWorkspace", "WorkspaceCapacityError",
+]
+
+__version__ = "0.1.0"

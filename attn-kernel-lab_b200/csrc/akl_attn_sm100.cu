@@ -1,0 +1,397 @@
+// Fused FP8 paged-prefill attention for sm_100a: tcgen05 kind::f8f6f4 MMAs with the S and O
+// accumulators in tensor memory, operand tiles brought in by bulk asynchronous copies,
+// exact online softmax (P x 448 fold, exact rescale skip) on a softmax warpgroup.
+//
+// It computes what the reference's mma.sync kernel computes
+// (src/attn_kernel_lab/csrc/fp8_prefill_attn.cu:220-681): per (128-row Q tile, q head)
+//   S  = Q8 K8^T                     e4m3 x e4m3 -> fp32            (:429-470)
+//   s  = S * qscale[row] * kscale[t], bottom-right causal bound      (:471-521)
+//   m' = max(m, rowmax);  alpha = ex2((m - m') log2e)                 (:528-541)
+//   p' = ex2(fma(s, log2e, log2 448 + log2 r_t - m' log2e))           (:542-553)
+//   l  = l alpha + sum(p') / r_t      (unrounded p')                  (:556-563)
+//   O  = O alpha  (skipped, exactly, when no row of the warp moved)   (:564-584)
+//   O += e4m3(p') V8                                                  (:591-611)
+//   out = bf16(fma(O, vscale / l, vmean)),  lse2 = m log2e + log2 l - log2 448   (:636-680)
+// per 64-key tile, in tile order -- the tile sequence is part of the operator because P is
+// rounded against the running maximum.
+//
+// CTA = 6 warps:  warps 0-3  softmax / O-rescale / epilogue (thread i owns query row i, which
+//                            is TMEM lane i),
+//                 warp 4     lane 0 issues the bulk copies; the warp owns TMEM alloc/free,
+//                 warp 5     lane 0 issues every tcgen05.mma.
+// Shared memory: Q tile 32 KiB; K and V^T 128-key pair tiles, two stages each (2 x 64 KiB);
+// P 2 x 16 KiB.  Tensor memory (512 columns): O = columns 0-255, S ping-pong = 256-383 /
+// 384-511.  QK^T runs at N = 128 keys per MMA group, softmax and PV at the operator's 64-key
+// tile granularity (two K=32 MMAs of N = 256 per tile).
+#include <atomic>
+
+#include "akl_common.cuh"
+#include "akl_sm100_ptx.cuh"
+
+namespace akl {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 192;
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = 32768;
+constexpr uint32_t kOffV = kOffK + 2 * 32768;
+constexpr uint32_t kOffP = kOffV + 2 * 32768;
+constexpr uint32_t kOffBar = kOffP + 2 * 16384;      // 196608
+constexpr uint32_t kOffVmean = kOffBar + 256;
+constexpr uint32_t kSmemBytes = kOffVmean + 1024 + 1024;  // + alignment slack
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColO = 0, kColS = 256;
+constexpr uint32_t kIdescQK = idesc_e4m3(128, 128);
+constexpr uint32_t kIdescPV = idesc_e4m3(128, 256);
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLog2_448 = 8.807354922057604f;
+constexpr long long kWaitCycles = 4000000000ll;      // ~2 s: a wait that long is a defect
+
+// barrier slots (8 bytes each)
+enum {
+  B_QFULL = 0,
+  B_KFULL = 1,   // [2]
+  B_KEMPTY = 3,  // [2]
+  B_VFULL = 5,   // [2]
+  B_VEMPTY = 7,  // [2]
+  B_SFULL = 9,   // [2]
+  B_SEMPTY = 11, // [2]
+  B_PFULL = 13,  // [2][2]
+  B_PVDONE = 17,
+  B_COUNT = 18
+};
+
+struct Ctx {
+  uint32_t bars;
+  int* status;
+  volatile int* abort_flag;   // shared memory
+};
+
+// Bounded mbarrier wait.  Returns false after ~2 s (or as soon as another thread of the CTA
+// gave up), having recorded AKL_ERR_TIMEOUT in the status word.
+__device__ __forceinline__ bool wait(const Ctx& c, int slot, uint32_t parity) {
+  const uint32_t bar = c.bars + slot * 8;
+  long long t0 = 0;
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 0xFFFu) == 0) {
+      if (t0 == 0) {
+        t0 = clock64();
+      } else if (*c.abort_flag || clock64() - t0 > kWaitCycles) {
+        *c.abort_flag = 1;
+        atomicCAS(c.status, 0, AKL_ERR_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void issue_qk(uint32_t smem, uint32_t tmem_s, int stage) {
+  const uint32_t qa = smem + kOffQ, kb = smem + kOffK + stage * 32768;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t off = (k >> 2) * kPlaneBytes + (k & 3) * 32;
+    mma_f8_ss(tmem_s, smem_desc_k128(qa + off), smem_desc_k128(kb + off), kIdescQK, k > 0);
+  }
+}
+
+__device__ __forceinline__ void issue_pv(uint32_t smem, uint32_t tmem_o, int buf, int half, bool accumulate) {
+  const uint32_t pa = smem + kOffP + buf * 16384 + half * 64;
+  const uint32_t vb = smem + kOffV + buf * 32768 + half * 64;
+#pragma unroll
+  for (int k = 0; k < 2; ++k)
+    mma_f8_ss(tmem_o, smem_desc_k128(pa + k * 32), smem_desc_k128(vb + k * 32), kIdescPV, (accumulate || k > 0) ? 1u : 0u);
+}
+
+template <bool kDump>
+__global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+  float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
+  const int h = blockIdx.y;
+  const int kvh = h / (g.Hq / g.Hkv);
+  const int m0 = qt * kQTile;
+
+  // keys this CTA visits, in local (this call's) positions
+  long long hi_ll = static_cast<long long>(g.prefix) + m0 + kQTile - g.kv_pos0;
+  const int hi = static_cast<int>(hi_ll < 0 ? 0 : (hi_ll > g.N ? g.N : hi_ll));
+  const int ntile = (hi + kTile - 1) / kTile;
+  const int npair = (ntile + 1) / 2;
+
+  Ctx ctx{smem + kOffBar, g.status, &abort_flag};
+
+  if (tid == 0) {
+    abort_flag = 0;
+    const uint32_t b = ctx.bars;
+    mbar_init(b + B_QFULL * 8, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(b + (B_KFULL + i) * 8, 1);
+      mbar_init(b + (B_KEMPTY + i) * 8, 1);
+      mbar_init(b + (B_VFULL + i) * 8, 1);
+      mbar_init(b + (B_VEMPTY + i) * 8, 1);
+      mbar_init(b + (B_SFULL + i) * 8, 1);
+      mbar_init(b + (B_SEMPTY + i) * 8, 128);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(b + (B_PFULL + i) * 8, 128);
+    mbar_init(b + B_PVDONE * 8, 1);
+    mbar_init_fence();
+    fence_async_smem();
+  }
+  if (warp == 4) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  if (tid < 128) {
+    sm_vmean[tid] = g.vmean[kvh * kD + tid];
+    sm_vmean[tid + 128] = g.vmean[kvh * kD + tid + 128];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0 && ntile > 0) {
+      const uint8_t* qsrc = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + qt) * kImageBytes;
+      const uint8_t* ksrc = g.k8 + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
+      const uint8_t* vsrc = g.v8t + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
+      mbar_expect_tx(ctx.bars + B_QFULL * 8, kImageBytes);
+      bulk_g2s(smem + kOffQ, qsrc, kImageBytes, ctx.bars + B_QFULL * 8);
+      for (int u = 0; u < npair; ++u) {
+        const int s = u & 1, n = u >> 1;
+        if (n >= 1 && !wait(ctx, B_KEMPTY + s, (n - 1) & 1)) break;
+        mbar_expect_tx(ctx.bars + (B_KFULL + s) * 8, kImageBytes);
+        bulk_g2s(smem + kOffK + s * 32768, ksrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
+                 ctx.bars + (B_KFULL + s) * 8);
+        if (n >= 1 && !wait(ctx, B_VEMPTY + s, (n - 1) & 1)) break;
+        mbar_expect_tx(ctx.bars + (B_VFULL + s) * 8, kImageBytes);
+        bulk_g2s(smem + kOffV + s * 32768, vsrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
+                 ctx.bars + (B_VFULL + s) * 8);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && ntile > 0) {
+      bool ok = wait(ctx, B_QFULL, 0) && wait(ctx, B_KFULL + 0, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(smem, tmem + kColS, 0);
+        tc_commit(ctx.bars + (B_SFULL + 0) * 8);
+        tc_commit(ctx.bars + (B_KEMPTY + 0) * 8);
+      }
+      for (int u = 0; ok && u < npair; ++u) {
+        if (u + 1 < npair) {
+          const int s = (u + 1) & 1, n = (u + 1) >> 1;
+          ok = wait(ctx, B_KFULL + s, n & 1);
+          if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + s, (n - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(smem, tmem + kColS + s * 128, s);
+          tc_commit(ctx.bars + (B_SFULL + s) * 8);
+          tc_commit(ctx.bars + (B_KEMPTY + s) * 8);
+        }
+        const int b = u & 1, par = (u >> 1) & 1;
+        ok = wait(ctx, B_VFULL + b, par);
+        for (int c = 0; ok && c < 2; ++c) {
+          const int j = 2 * u + c;
+          if (j >= ntile) break;
+          ok = wait(ctx, B_PFULL + b * 2 + c, par);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(smem, tmem + kColO, b, c, j > 0);
+          tc_commit(ctx.bars + B_PVDONE * 8);
+        }
+        if (ok) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warpgroup
+    const int row = tid;                      // query row inside the tile == TMEM lane
+    const int grow = m0 + row;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    long long lim_ll = static_cast<long long>(g.prefix) + grow - g.kv_pos0;
+    const int limit = static_cast<int>(lim_ll > g.N - 1 ? g.N - 1 : lim_ll);   // last visible local key (may be < 0)
+    const float qs = g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
+    const float* kscale = g.kscale + kvh * g.ntiles_cap;
+    const float* vlog2r = g.vlog2r + kvh * g.ntiles_cap;
+    const float* vinvr = g.vinvr + kvh * g.ntiles_cap;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < ntile; ++j) {
+      const int u = j >> 1, c = j & 1, b = u & 1;
+      if (c == 0) {
+        if (!wait(ctx, B_SFULL + b, (u >> 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+      }
+      __syncwarp();
+      uint32_t sr[64];
+      {
+        uint32_t lo32[32], hi32[32];
+        const uint32_t ta = lane_base + kColS + b * 128 + c * 64;
+        tmem_ld32(ta, lo32);
+        tmem_ld32(ta + 32, hi32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { sr[i] = lo32[i]; sr[32 + i] = hi32[i]; }
+      }
+      if (c == 1 || j == ntile - 1) {
+        tc_fence_before();
+        mbar_arrive(ctx.bars + (B_SEMPTY + b) * 8);
+      }
+      if (kDump) {
+        float* dst = g.dbg_s + ((((static_cast<size_t>(h) * g.mtiles + qt) * g.nt + j) * kQTile + row) * kTile);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(sr[i]);
+      }
+      const float sc = qs * __ldg(kscale + j);
+      const int rem = limit - j * kTile;
+      float s[64];
+      float rowmax = -INFINITY;
+      if (rem >= kTile - 1) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          s[i] = __uint_as_float(sr[i]) * sc;
+          rowmax = fmaxf(rowmax, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float v = __uint_as_float(sr[i]) * sc;
+          s[i] = (i <= rem) ? v : -INFINITY;
+          rowmax = fmaxf(rowmax, s[i]);
+        }
+      }
+      const float m_new = fmaxf(m, rowmax);
+      const float alpha = (m == -INFINITY) ? 0.f : ex2((m - m_new) * kLog2e);
+      const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + __ldg(vlog2r + j)) - m_new * kLog2e;
+      m = m_new;
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        s[i] = ex2(fmaf(s[i], kLog2e, pc));
+        part[i & 3] += s[i];
+      }
+      l = l * alpha + ((part[0] + part[1]) + (part[2] + part[3])) * __ldg(vinvr + j);
+
+      // Every thread observes every phase of the PV-done barrier, in order: a parity wait
+      // is only meaningful while the waiter is at most one phase behind, and a thread that
+      // skipped phases (no rescale for a few tiles) could otherwise see a stale parity as
+      // "done" and rescale O under a running MMA.
+      if (j > 0 && !wait(ctx, B_PVDONE, (j - 1) & 1)) { ok = false; break; }
+      // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
+      __syncwarp();
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t o[32];
+          tmem_ld32(lane_base + kColO + ch * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(lane_base + kColO + ch * 32, o);
+        }
+        tmem_wait_st();
+      }
+
+      // P -> E4M3 -> shared memory (128-byte-swizzled A operand of the PV MMA)
+      const uint32_t prow = smem + kOffP + b * 16384;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int i0 = q4 * 16;
+        const uint32_t w0 = cvt_e4m3x4(s[i0 + 0], s[i0 + 1], s[i0 + 2], s[i0 + 3]);
+        const uint32_t w1 = cvt_e4m3x4(s[i0 + 4], s[i0 + 5], s[i0 + 6], s[i0 + 7]);
+        const uint32_t w2 = cvt_e4m3x4(s[i0 + 8], s[i0 + 9], s[i0 + 10], s[i0 + 11]);
+        const uint32_t w3 = cvt_e4m3x4(s[i0 + 12], s[i0 + 13], s[i0 + 14], s[i0 + 15]);
+        st_shared_v4(prow + swz128(row, c * 64 + i0), w0, w1, w2, w3);
+        if (kDump) {
+          uint8_t* dst = g.dbg_p + ((((static_cast<size_t>(h) * g.mtiles + qt) * g.nt + j) * kQTile + row) * kTile);
+          *reinterpret_cast<uint4*>(dst + i0) = make_uint4(w0, w1, w2, w3);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(ctx.bars + (B_PFULL + b * 2 + c) * 8);
+    }
+
+    // ---------------------------------------------------------- epilogue
+    if (ok && ntile > 0) ok = wait(ctx, B_PVDONE, (ntile - 1) & 1);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = (l > 0.f) ? g.vscale[kvh] / l : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(g.out) + (static_cast<size_t>(grow) * g.Hq + h) * kD;
+#pragma unroll 1
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t o[32];
+        if (ntile > 0) {
+          tmem_ld32(lane_base + kColO + ch * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (grow < g.T) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = v4 * 8 + e * 2;
+              const float a = fmaf(__uint_as_float(o[i]), inv_l, sm_vmean[ch * 32 + i]);
+              const float bb = fmaf(__uint_as_float(o[i + 1]), inv_l, sm_vmean[ch * 32 + i + 1]);
+              __nv_bfloat162 t = __floats2bfloat162_rn(a, bb);
+              pk[e] = *reinterpret_cast<uint32_t*>(&t);
+            }
+            *reinterpret_cast<uint4*>(orow + ch * 32 + v4 * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+      }
+      if (g.lse_out != nullptr && grow < g.T) {
+        g.lse_out[static_cast<size_t>(grow) * g.Hq + h] =
+            (l > 0.f) ? fmaf(m, kLog2e, log2f(l) - kLog2_448) : -INFINITY;
+      }
+      tc_fence_before();
+    }
+  }
+
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_attention(const Geom& g, cudaStream_t s, bool dump) {
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { note_cuda_error(e, "cudaGetDevice"); return AKL_ERR_CUDA; }
+  if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+    // idempotent, so a race between host threads only repeats the call
+    e = cudaFuncSetAttribute(attn_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(attn)"); return AKL_ERR_CUDA; }
+    if (dev < 64) configured[dev].store(true, std::memory_order_release);
+  }
+  dim3 grid(g.mtiles, g.Hq);
+  if (dump)
+    attn_sm100_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(g);
+  else
+    attn_sm100_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(g);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { note_cuda_error(e, "attn_sm100_kernel"); return AKL_ERR_CUDA; }
+  return AKL_OK;
+}
+
+}  // namespace akl

@@ -1,0 +1,375 @@
+// Preprocessing kernels: paged gather, K/V statistics, K/V transform + quantisation, Q
+// rotation + quantisation.  They replace the tensor-library pipeline of the reference's
+// src/attn_kernel_lab/quant.py:433-695 (about 14 launches per call) with five launches.
+//
+// All arithmetic that decides a quantised byte is plain IEEE fp32 in a fixed order; this
+// file is compiled with -fmad=false so no multiply-add is ever contracted.
+//
+// Work decomposition (HBM-bound byte work, so: 16-byte coalesced loads, one full 512-byte
+// row per warp-load, 64 KiB in flight per CTA, grids of nt*Hkv CTAs):
+//   CTA  = one 64-row tile of one kv head, 256 threads;
+//   warp = 8 consecutive rows of the tile;
+//   lane = 8 consecutive channels (one 16-byte load per row).
+#include "akl_common.cuh"
+
+namespace akl {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------
+// 1. per-tile channel sums of K and V, per-tile channel min/max of V
+//    (reference pass 1, quant.py:532-568)
+// ---------------------------------------------------------------------------
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads) kv_tile_stats_kernel(Geom g) {
+  __shared__ float sm_k[8][kD];
+  __shared__ float sm_v[8][kD];
+  __shared__ float sm_mx[8][kD];
+  __shared__ float sm_mn[8][kD];
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = t * kTile + w * 8;
+
+  // pool rows of this warp's 8 positions
+  long long pr = 0;
+  if (lane < 8 && row0 + lane < g.N) pr = load_idx<IDX_DTYPE>(g.idx, row0 + lane);
+  uint4 kraw[8], vraw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    long long p = __shfl_sync(0xffffffffu, pr, i);
+    if (row0 + i < g.N) {
+      size_t off = (static_cast<size_t>(p) * g.Hkv + kvh) * kD + lane * 8;
+      kraw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.k_pool) + off));
+      vraw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.v_pool) + off));
+    }
+  }
+  float ks[8], vs[8], mx[8], mn[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) { ks[c] = 0.f; vs[c] = 0.f; mx[c] = -INFINITY; mn[c] = INFINITY; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (row0 + i < g.N) {
+      float kx[8], vx[8];
+      unpack8<KV_DTYPE>(kraw[i], kx);
+      unpack8<KV_DTYPE>(vraw[i], vx);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        ks[c] = __fadd_rn(ks[c], kx[c]);
+        vs[c] = __fadd_rn(vs[c], vx[c]);
+        mx[c] = fmaxf(mx[c], vx[c]);
+        mn[c] = fminf(mn[c], vx[c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    sm_k[w][lane * 8 + c] = ks[c];
+    sm_v[w][lane * 8 + c] = vs[c];
+    sm_mx[w][lane * 8 + c] = mx[c];
+    sm_mn[w][lane * 8 + c] = mn[c];
+  }
+  __syncthreads();
+  // the eight 8-row run sums are added in run order
+  const int c = threadIdx.x;
+  float sk = 0.f, sv = 0.f, vmx = -INFINITY, vmn = INFINITY;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    sk = __fadd_rn(sk, sm_k[r][c]);
+    sv = __fadd_rn(sv, sm_v[r][c]);
+    vmx = fmaxf(vmx, sm_mx[r][c]);
+    vmn = fminf(vmn, sm_mn[r][c]);
+  }
+  const size_t gt = static_cast<size_t>(g.tile0_global + t);
+  g.ktsum[(gt * g.Hkv + kvh) * kD + c] = sk;
+  g.vtsum[(gt * g.Hkv + kvh) * kD + c] = sv;
+  g.vtmax[(static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD + c] = vmx;
+  g.vtmin[(static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD + c] = vmn;
+}
+
+// ---------------------------------------------------------------------------
+// 2. channel means (ordered: tiles inside a 32768-row slab, then slabs) and the
+//    centred per-tile V amax  (quant.py:566-581)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) kv_means_kernel(Geom g) {
+  __shared__ float sm_vmean[kD];
+  __shared__ float sm_wmax[8];
+  const int kvh = blockIdx.x, c = threadIdx.x;
+  const int ntg = g.ntiles_global;
+  float ktot = 0.f, vtot = 0.f;
+  for (int s0 = 0; s0 < ntg; s0 += kSlabTiles) {
+    const int s1 = min(s0 + kSlabTiles, ntg);
+    float kslab = 0.f, vslab = 0.f;
+    for (int t = s0; t < s1; ++t) {
+      kslab = __fadd_rn(kslab, g.ktsum[(static_cast<size_t>(t) * g.Hkv + kvh) * kD + c]);
+      vslab = __fadd_rn(vslab, g.vtsum[(static_cast<size_t>(t) * g.Hkv + kvh) * kD + c]);
+    }
+    ktot = __fadd_rn(ktot, kslab);
+    vtot = __fadd_rn(vtot, vslab);
+  }
+  const float denom = static_cast<float>(max(g.n_total, 1));
+  const float vmean = __fdiv_rn(vtot, denom);
+  const float kmean = (g.flags & AKL_FLAG_CENTER_K) ? __fdiv_rn(ktot, denom) : 0.f;
+  g.kmean[kvh * kD + c] = kmean;
+  g.vmean[kvh * kD + c] = vmean;
+  sm_vmean[c] = vmean;
+  __syncthreads();
+  // vam[t] = max_c max(fl(mx - mean), fl(mean - mn)); one warp per tile
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float wmax = 0.f;
+  for (int t = w; t < g.nt; t += 8) {
+    const float* pmx = g.vtmax + (static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD;
+    const float* pmn = g.vtmin + (static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD;
+    float a = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int ch = lane + 32 * j;
+      const float m = sm_vmean[ch];
+      a = fmaxf(a, fmaxf(__fsub_rn(pmx[ch], m), __fsub_rn(m, pmn[ch])));
+    }
+    a = warp_max(a);
+    if (lane == 0) g.vam[kvh * g.ntiles_cap + t] = a;
+    wmax = fmaxf(wmax, a);
+  }
+  if (lane == 0) sm_wmax[w] = wmax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = 0.f;
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, sm_wmax[i]);
+    g.vsmax[kvh] = m;   // raw, unclamped: a MAX all-reduce may combine ranks here
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 3. per-tile V scales and the fold arrays  (quant.py:576-584, :673-679)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) kv_scales_kernel(Geom g) {
+  const int kvh = blockIdx.x;
+  const float vsm = fmaxf(g.vsmax[kvh], 1e-8f);
+  const float floor_ = __fdiv_rn(vsm, 16.0f);
+  for (int t = threadIdx.x; t < g.nt; t += blockDim.x) {
+    const int o = kvh * g.ntiles_cap + t;
+    const float vst = __fdiv_rn(fmaxf(g.vam[o], floor_), kFp8Max);
+    float r = __fdiv_rn(__fmul_rn(vst, kFp8Max), vsm);
+    r = fminf(fmaxf(r, 0.0625f), 1.0f);
+    g.vst[o] = vst;
+    g.vlog2r[o] = log2f(r);
+    g.vinvr[o] = __fdiv_rn(1.0f, r);
+  }
+  if (threadIdx.x == 0) g.vscale[kvh] = __fdiv_rn(vsm, kFp8Max);
+}
+
+// ---------------------------------------------------------------------------
+// 4. K: gather, centre, rotate, per-tile amax, E4M3  -> swizzled [pair][2][128][128] image
+//    V: gather, centre, per-tile scale, E4M3, transpose -> swizzled [pair][256][128] image
+//    (quant.py:589-668).  blockIdx.z: 0 = K, 1 = V.
+// ---------------------------------------------------------------------------
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
+  constexpr int kVRow = 80;                       // padded 64-byte row, keeps 16 B alignment
+  __shared__ float sm_red[8];
+  __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const bool is_v = blockIdx.z == 1;
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = t * kTile + w * 8;
+  const void* pool = is_v ? g.v_pool : g.k_pool;
+
+  long long pr = 0;
+  if (lane < 8 && row0 + lane < g.N) pr = load_idx<IDX_DTYPE>(g.idx, row0 + lane);
+  uint4 raw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    long long p = __shfl_sync(0xffffffffu, pr, i);
+    if (row0 + i < g.N) {
+      size_t off = (static_cast<size_t>(p) * g.Hkv + kvh) * kD + lane * 8;
+      raw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(pool) + off));
+    }
+  }
+  float mean[8];
+  {
+    const float* mp = (is_v ? g.vmean : g.kmean) + kvh * kD + lane * 8;
+    const float4 m0 = *reinterpret_cast<const float4*>(mp);
+    const float4 m1 = *reinterpret_cast<const float4*>(mp + 4);
+    mean[0] = m0.x; mean[1] = m0.y; mean[2] = m0.z; mean[3] = m0.w;
+    mean[4] = m1.x; mean[5] = m1.y; mean[6] = m1.z; mean[7] = m1.w;
+  }
+  const bool center = is_v || (g.flags & AKL_FLAG_CENTER_K);
+  const bool rotate = !is_v && (g.flags & AKL_FLAG_ROTATE);
+
+  float x[8][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (row0 + i < g.N) {          // warp-uniform
+      unpack8<KV_DTYPE>(raw[i], x[i]);
+      if (center) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) x[i][c] = __fsub_rn(x[i][c], mean[c]);
+      }
+      if (rotate) fwht256(x[i], lane);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[i][c]));
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) x[i][c] = 0.f;   // padding rows are exact zeros
+    }
+  }
+
+  float scale;
+  if (!is_v) {
+    amax = warp_max(amax);
+    if (lane == 0) sm_red[w] = amax;
+    __syncthreads();
+    float a = sm_red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) a = fmaxf(a, sm_red[i]);
+    a = fmaxf(a, 1e-8f);
+    scale = __fdiv_rn(a, kFp8Max);
+    if (threadIdx.x == 0) g.kscale[kvh * g.ntiles_cap + t] = scale;
+  } else {
+    scale = g.vst[kvh * g.ntiles_cap + t];
+  }
+
+  uint32_t lo[8], hi[8];          // bytes of channels 0-3 / 4-7 of each row
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float y[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[i][c], scale);
+    lo[i] = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
+    hi[i] = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+  }
+
+  const int pair = t >> 1, half = t & 1;
+  if (!is_v) {
+    uint8_t* img = g.k8 + (static_cast<size_t>(kvh) * g.npairs_cap + pair) * kImageBytes;
+    const int plane = lane >> 4;
+    const uint32_t cbyte = (lane & 15) * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t r = half * 64 + w * 8 + i;
+      *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(r, cbyte)) = make_uint2(lo[i], hi[i]);
+    }
+  } else {
+    // transpose through shared memory: sm_vt[d][key]
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t b0 = 0, b1 = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t src0 = (c < 4) ? lo[i] : hi[i];
+        const uint32_t src1 = (c < 4) ? lo[i + 4] : hi[i + 4];
+        b0 |= ((src0 >> (8 * (c & 3))) & 0xFFu) << (8 * i);
+        b1 |= ((src1 >> (8 * (c & 3))) & 0xFFu) << (8 * i);
+      }
+      *reinterpret_cast<uint2*>(sm_vt + (lane * 8 + c) * kVRow + w * 8) = make_uint2(b0, b1);
+    }
+    __syncthreads();
+    const int d = threadIdx.x;
+    uint8_t* img = g.v8t + (static_cast<size_t>(kvh) * g.npairs_cap + pair) * kImageBytes;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = *reinterpret_cast<const uint4*>(sm_vt + d * kVRow + j * 16);
+      *reinterpret_cast<uint4*>(img + swz128(d, half * 64 + j * 16)) = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 5. Q: rotate, per-row amax, E4M3, scale*sm_scale  (quant.py:433-480)
+//    one warp per (head, padded row); rows >= T are zero bytes with the clamp scale
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) quantize_q_kernel(Geom g) {
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mpad = g.mtiles * kQTile;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + w;
+  if (item >= static_cast<long long>(g.Hq) * mpad) return;
+  const int h = static_cast<int>(item / mpad), r = static_cast<int>(item % mpad);
+  float x[8];
+  float amax = 0.f;
+  if (r < g.T) {
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(g.q) + (static_cast<size_t>(r) * g.Hq + h) * kD + lane * 8;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+    unpack8<AKL_KV_BF16>(raw, x);
+    if (g.flags & AKL_FLAG_ROTATE) fwht256(x, lane);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[c]));
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) x[c] = 0.f;
+  }
+  amax = fmaxf(warp_max(amax), 1e-8f);
+  const float scale = __fdiv_rn(amax, kFp8Max);
+  float y[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[c], scale);
+  const uint32_t lo = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
+  const uint32_t hi = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+  const int tile = r >> 7, rr = r & 127, plane = lane >> 4;
+  uint8_t* img = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + tile) * kImageBytes;
+  *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(rr, (lane & 15) * 8)) = make_uint2(lo, hi);
+  if (lane == 0) g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + r] = __fmul_rn(scale, g.sm_scale);
+}
+
+}  // namespace
+
+#define AKL_LAUNCH_CHECK(where)                    \
+  do {                                             \
+    cudaError_t e_ = cudaGetLastError();           \
+    if (e_ != cudaSuccess) {                       \
+      note_cuda_error(e_, where);                  \
+      return AKL_ERR_CUDA;                         \
+    }                                              \
+  } while (0)
+
+int launch_kv_tile_stats(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s) {
+  dim3 grid(g.nt, g.Hkv);
+  if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
+    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+  else if (kv_dtype == AKL_KV_BF16)
+    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+  else if (idx_dtype == AKL_IDX_I64)
+    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+  else
+    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+  AKL_LAUNCH_CHECK("kv_tile_stats");
+  return AKL_OK;
+}
+
+int launch_kv_means(const Geom& g, cudaStream_t s) {
+  kv_means_kernel<<<g.Hkv, kThreads, 0, s>>>(g);
+  AKL_LAUNCH_CHECK("kv_means");
+  return AKL_OK;
+}
+
+int launch_kv_scales(const Geom& g, cudaStream_t s) {
+  kv_scales_kernel<<<g.Hkv, kThreads, 0, s>>>(g);
+  AKL_LAUNCH_CHECK("kv_scales");
+  return AKL_OK;
+}
+
+int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s) {
+  dim3 grid(g.nt, g.Hkv, 2);
+  if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
+    kv_transform_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+  else if (kv_dtype == AKL_KV_BF16)
+    kv_transform_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+  else if (idx_dtype == AKL_IDX_I64)
+    kv_transform_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+  else
+    kv_transform_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+  AKL_LAUNCH_CHECK("kv_transform");
+  return AKL_OK;
+}
+
+int launch_quantize_q(const Geom& g, cudaStream_t s) {
+  const long long items = static_cast<long long>(g.Hq) * g.mtiles * kQTile;
+  const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
+  quantize_q_kernel<<<blocks, kThreads, 0, s>>>(g);
+  AKL_LAUNCH_CHECK("quantize_q");
+  return AKL_OK;
+}
+
+}  // namespace akl

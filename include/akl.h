@@ -1,0 +1,172 @@
+/*
+ * akl.h -- C ABI of libakl_sm100a.so: fused FP8 paged EXTEND/prefill attention for
+ * NVIDIA B200 (sm_100a).  Head dimension 256, page size 1, GQA n:4, E4M3 Q/K/V/P.
+ *
+ * This is the boundary a host binds instead of the reference's pybind11 torch
+ * extension (one function taking 13 tensors, src/attn_kernel_lab/csrc/
+ * fp8_prefill_attn.cu:689-696 and :812-824) and instead of the ~14 tensor-library
+ * launches of its preprocessing (src/attn_kernel_lab/quant.py:433-695).
+ *
+ * Conventions (every entry point):
+ *   - plain C types, raw device pointers, byte sizes; no tensor-library types;
+ *   - returns 0 (AKL_OK) or a negative AKL_ERR_* code, never throws, never traps;
+ *   - enqueues on the caller's stream and returns; never synchronises
+ *     (docs/OPERATOR_CONTRACT.md:210-211 of the reference);
+ *   - allocates no device memory: the caller owns inputs, outputs and the workspace
+ *     (docs/OPERATOR_CONTRACT.md:204-221), whose addresses may be baked into a
+ *     CUDA graph;
+ *   - device-side waits are bounded; a wait that runs out stores a nonzero code in
+ *     the workspace status word (akl_ws_layout_t.off_status) and the kernel returns.
+ */
+#ifndef AKL_H_
+#define AKL_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AKL_ABI_VERSION 1
+#define AKL_HEAD_DIM 256
+#define AKL_KV_TILE 64   /* quantisation tile along the kv axis (reference BLK, quant.py:80) */
+#define AKL_Q_TILE 128   /* query rows per CTA and padding granule (reference MPAD, quant.py:86) */
+#define AKL_STAT_SLAB 32768 /* statistics slab in rows (reference SLAB, quant.py:87) */
+
+enum {
+  AKL_OK = 0,
+  AKL_ERR_INVALID = -1,    /* null pointer, non-positive size, bad enum */
+  AKL_ERR_UNSUPPORTED = -2,/* outside the surface: head_dim, heads, flags */
+  AKL_ERR_CAPACITY = -3,   /* request does not fit the workspace it was given */
+  AKL_ERR_CUDA = -4,       /* a CUDA runtime call failed; see akl_last_cuda_error() */
+  AKL_ERR_ALIGN = -5,      /* pointer not aligned as required */
+  AKL_ERR_TIMEOUT = -6     /* (status word only) a bounded device wait ran out */
+};
+
+enum { AKL_KV_BF16 = 0, AKL_KV_FP16 = 1 };
+enum { AKL_IDX_I64 = 0, AKL_IDX_I32 = 1 };
+
+/* akl_call_t.flags */
+#define AKL_FLAG_ROTATE 1u    /* Hadamard-rotate Q and K (reference kwarg rotate, ops.py:497) */
+#define AKL_FLAG_CENTER_K 2u  /* subtract the K channel mean (reference kwarg center_k, ops.py:498) */
+
+/* Capacity plan: the maxima a workspace is laid out for.
+ * Replaces quant.FP8PrefillWorkspace.reserve / CapacityPlan (quant.py:175-196, :253-336). */
+typedef struct akl_plan {
+  int32_t max_kv_len;   /* largest idx length of any request */
+  int32_t max_q_len;    /* largest extend length */
+  int32_t q_heads;
+  int32_t kv_heads;
+} akl_plan_t;
+
+/* Byte offsets of every named region inside ONE caller-owned allocation.
+ * Replaces the named buffers of quant.py:303-321. */
+typedef struct akl_ws_layout {
+  uint64_t total_bytes;
+  int32_t npairs;       /* ceil(max_kv_len / 128): 128-key tile pairs per kv head */
+  int32_t ntiles;       /* 2 * npairs: capacity in 64-key tiles */
+  int32_t mtiles;       /* ceil(max_q_len / 128) */
+  int32_t reserved_;
+  uint64_t off_q8;      /* [Hq][mtiles][2][128][128] u8, 128B-swizzled tile images */
+  uint64_t off_qscale;  /* [Hq][mtiles*128] f32 */
+  uint64_t off_k8;      /* [Hkv][npairs][2][128][128] u8, swizzled */
+  uint64_t off_v8t;     /* [Hkv][npairs][256][128] u8, d-major, swizzled */
+  uint64_t off_kscale;  /* [Hkv][ntiles] f32 */
+  uint64_t off_vst;     /* [Hkv][ntiles] f32 */
+  uint64_t off_vlog2r;  /* [Hkv][ntiles] f32 */
+  uint64_t off_vinvr;   /* [Hkv][ntiles] f32 */
+  uint64_t off_vam;     /* [Hkv][ntiles] f32 centred per-tile amax */
+  uint64_t off_vscale;  /* [Hkv] f32 */
+  uint64_t off_vsmax;   /* [Hkv] f32 raw max of vam (a MAX all-reduce may run on it) */
+  uint64_t off_kmean;   /* [Hkv][256] f32 */
+  uint64_t off_vmean;   /* [Hkv][256] f32 */
+  uint64_t off_ktsum;   /* [Hkv][ntiles][256] f32 per-tile channel sums of K */
+  uint64_t off_vtsum;   /* [Hkv][ntiles][256] f32 */
+  uint64_t off_vtmax;   /* [Hkv][ntiles][256] f32 */
+  uint64_t off_vtmin;   /* [Hkv][ntiles][256] f32 */
+  uint64_t off_status;  /* [64] i32; word 0 = first device error code, 0 when clean */
+} akl_ws_layout_t;
+
+/* One rectangular request == one call of the reference operator
+ * (ops.prefill_extend, src/attn_kernel_lab/ops.py:485-609). */
+typedef struct akl_call {
+  const void* q;        /* [T][Hq][256] bf16, contiguous */
+  const void* k_pool;   /* [pool_rows][Hkv][256] bf16 | fp16 */
+  const void* v_pool;
+  const void* idx;      /* [N] i64 | i32 pool rows in position order (values unchecked) */
+  void* out;            /* [T][Hq][256] bf16 */
+  float* lse_out;       /* [T][Hq] f32 base-2 log-sum-exp, or NULL */
+  void* workspace;      /* base of the allocation described by `plan` */
+  uint64_t workspace_bytes;
+  akl_plan_t plan;      /* what the workspace was laid out for */
+  int32_t T;            /* extend length (q rows), >= 1 */
+  int32_t N;            /* gathered kv length, >= 1 */
+  int32_t prefix;       /* cached positions, 0 <= prefix <= N - T (+ kv_pos0 for a split) */
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t kv_dtype;     /* AKL_KV_* */
+  int32_t idx_dtype;    /* AKL_IDX_* */
+  uint32_t flags;       /* AKL_FLAG_* */
+  float sm_scale;       /* folded into the Q scales (quant.py:479) */
+  /* KV-axis split (multi-GPU long request): this call's idx covers global positions
+   * [kv_pos0, kv_pos0 + N); `prefix` stays global; statistics are made global by the
+   * caller between the phase calls below.  0 / N_total==N for an unsplit request. */
+  int32_t kv_pos0;      /* multiple of 64 */
+  int32_t n_total;      /* global kv length (the divisor of the channel means); 0 means N */
+  int32_t tile0_global; /* index of this call's first 64-row tile in the global tile order */
+  int32_t ntiles_global;/* number of global 64-row tiles present in the tile-sum arrays; 0 = local */
+} akl_call_t;
+
+/* (O, lse2) partial-state merge for a KV-axis split: out = sum_i 2^(lse_i - lse) O_i,
+ * lse = log2 sum_i 2^lse_i.  New: the reference exposes base-2 LSE for this purpose
+ * (docs/OPERATOR_CONTRACT.md:57,238-242) but ships no merge. */
+typedef struct akl_merge {
+  const void* const* parts_o;     /* device array of nparts pointers to [rows][256] bf16 */
+  const float* const* parts_lse;  /* device array of nparts pointers to [rows] f32 */
+  void* out;                      /* [rows][256] bf16 */
+  float* lse_out;                 /* [rows] f32 or NULL */
+  int32_t nparts;
+  int32_t rows;                   /* T * Hq */
+} akl_merge_t;
+
+int akl_abi_version(void);
+const char* akl_strerror(int code);
+const char* akl_last_cuda_error(void);
+
+/* Workspace geometry.  Pure host arithmetic; no CUDA call. */
+int akl_workspace_layout(const akl_plan_t* plan, akl_ws_layout_t* out);
+
+/* The whole operator for one request: statistics, transform, attention, output write.
+ * Replaces gather_quantize_kv + quantize_q + ext.fp8_prefill_attn + the final
+ * permute-copy (ops.py:563-609). */
+int akl_prefill_extend(const akl_call_t* call, void* stream);
+
+/* The same work as separate phases, for callers that must make the statistics global
+ * between them (KV-axis split) or want the quantised artifacts alone:
+ *   1 akl_kv_tile_stats      per-tile K/V channel sums + V min/max   (quant.py:532-568)
+ *   2 akl_kv_means           ordered reduction -> kmean, vmean; vam, vsmax (quant.py:566-581)
+ *   3 akl_kv_scales          vst, r_t, vlog2r, vinvr, vscale          (quant.py:582-584, :673-679)
+ *   4 akl_kv_transform       centre, rotate, quantise K and V         (quant.py:589-668)
+ *   5 akl_quantize_q         rotate + per-row quantise Q              (quant.py:433-480)
+ *   6 akl_attention          the fused kernel                         (fp8_prefill_attn.cu:220-681)
+ */
+int akl_kv_tile_stats(const akl_call_t* call, void* stream);
+int akl_kv_means(const akl_call_t* call, void* stream);
+int akl_kv_scales(const akl_call_t* call, void* stream);
+int akl_kv_transform(const akl_call_t* call, void* stream);
+int akl_quantize_q(const akl_call_t* call, void* stream);
+int akl_attention(const akl_call_t* call, void* stream);
+
+/* Diagnostic twin of akl_attention: same launch, and additionally stores, for every
+ * (q head, 128-row Q tile, 64-key tile, row), the 64 raw fp32 QK^T accumulators and the 64
+ * E4M3 P bytes fed to the PV MMA.  s_dump / p_dump: [Hq][ceil(T/128)][ceil(N/64)][128][64].
+ * Plays the role of the reference's score/probability probes (tests/kernel/
+ * test_divergence_hunting.py); parity tests use it to check P byte-for-byte. */
+int akl_attention_dump(const akl_call_t* call, float* s_dump, uint8_t* p_dump, void* stream);
+
+int akl_merge_states(const akl_merge_t* m, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKL_H_ */
