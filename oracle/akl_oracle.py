@@ -281,11 +281,16 @@ def preprocess_kv(
     center_k: bool = True,
     kmean: np.ndarray | None = None,
     vmean: np.ndarray | None = None,
+    vsmax_raw: np.ndarray | None = None,
 ) -> KVPack:
     """Statistics, K transform, V transform and fold arrays (quant.py:483-695).
 
     `kmean` / `vmean` override the channel means (used to pin every later step
-    against the reference, whose mean reduction order cannot be restated)."""
+    against the reference, whose mean reduction order cannot be restated, and to
+    hand a KV-axis split the request-wide means).  `vsmax_raw` overrides the
+    per-head maximum of the centred per-tile V amax (request-wide for a split).
+    The raw maximum this slice would have produced is stored on the result as
+    `vsmax_local`."""
     k = np.asarray(k, dtype=np.float32)
     v = np.asarray(v, dtype=np.float32)
     N, KVH, D = k.shape
@@ -310,7 +315,9 @@ def preprocess_kv(
         vtmn[:, t] = rows.min(axis=1)
     vam = np.maximum((vtmx - vmean[:, None, :]).astype(np.float32),
                      (vmean[:, None, :] - vtmn).astype(np.float32)).max(axis=2)
-    vsmax = np.maximum(vam.max(axis=1), F32(1e-8)).astype(np.float32)
+    vsmax_local = vam.max(axis=1).astype(np.float32)
+    vsmax = np.maximum(vsmax_local if vsmax_raw is None else np.asarray(vsmax_raw, np.float32),
+                       F32(1e-8)).astype(np.float32)
     vst = (np.maximum(vam, (vsmax[:, None] / F32(16.0)).astype(np.float32))
            / F32(FP8_MAX)).astype(np.float32)
 
@@ -339,8 +346,10 @@ def preprocess_kv(
     vlog2r = np.log2(r).astype(np.float32)
     vinvr = (F32(1.0) / r).astype(np.float32)
     vscale = (vsmax / F32(FP8_MAX)).astype(np.float32)
-    return KVPack(k8=k8, kscale=kscale, kmean=kmean, v8=v8, vst=vst, vscale=vscale,
+    pack = KVPack(k8=k8, kscale=kscale, kmean=kmean, v8=v8, vst=vst, vscale=vscale,
                   vlog2r=vlog2r, vinvr=vinvr, vmean=vmean, n=N)
+    pack.vsmax_local = vsmax_local
+    return pack
 
 
 # --------------------------------------------------------------------------
@@ -357,6 +366,7 @@ def attention(
     heads=None,
     kv_lo: int = 0,
     kv_hi: int | None = None,
+    collect_p: dict | None = None,
 ):
     """The intended quantised operator in float64.
 
@@ -369,7 +379,8 @@ def attention(
 
     `heads` selects a subset of query heads (default all).  `kv_lo:kv_hi`
     (multiples of 64) restricts the tiles visited -- the per-split operator of a
-    KV-axis split; statistics inside `kv` stay global."""
+    KV-axis split; statistics inside `kv` stay global.  `collect_p`, when a dict, receives
+    the E4M3 P bytes of every visited tile as collect_p[(head, tile)] = uint8 [T, width]."""
     H = qp.q8.shape[0]
     KVH, npad, D = kv.k8.shape
     n = kv.n
@@ -404,7 +415,10 @@ def attention(
                 p = np.where(visible, np.exp(s - m_new[:, None]), 0.0)
             alpha = np.where(np.isneginf(m_new), 1.0, alpha)   # row not started yet
             r_t = 1.0 / float(kv.vinvr[kvh, t])
-            p8 = dec[e4m3_encode((p * (FP8_MAX * r_t)).astype(np.float32))]
+            p8_bytes = e4m3_encode((p * (FP8_MAX * r_t)).astype(np.float32))
+            if collect_p is not None:
+                collect_p[(h, t)] = p8_bytes
+            p8 = dec[p8_bytes]
             vf = dec[kv.v8[kvh, lo:lo + width]]
             acc = acc * alpha[:, None] + p8 @ vf
             l = l * alpha + p.sum(axis=1) * FP8_MAX

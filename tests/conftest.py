@@ -1,0 +1,37 @@
+"""Test configuration: the `gpu` marker, import paths, and shared helpers.
+
+`-m "not gpu"` covers the oracle against the golden vectors, the host logic and the C-ABI
+surface; `-m gpu` holds the parity tests proper, which call the CUDA path through the C ABI.
+The oracle (oracle/akl_oracle.py) is imported here as the checker only.
+"""
+import pathlib
+import sys
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+for p in (ROOT, ROOT / "tests", ROOT / "oracle"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (NVIDIA B200, sm_100a)")
+
+
+@pytest.fixture(scope="session")
+def pkg():
+    import __graft_entry__ as entry
+
+    package = entry.package()
+    package.build()
+    return package
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch.device("cuda:0")
