@@ -256,4 +256,5 @@ def test_plain_attention_envelope():
     got = O.reference(q, k, v, case["prefix"], sm_scale=case["sm_scale"])
     want = O.plain_attention(q, k, v, case["prefix"], case["sm_scale"])
     rel = np.linalg.norm((got - want).reshape(-1, 256), axis=1) / np.linalg.norm(want.reshape(-1, 256), axis=1)
-    assert rel.mean() < 0.08 and rel.max() < 0.3      # FP8 QK on outlier channels; not a parity bar
+    # FP8 QK on x16 outlier channels; fidelity to unquantised attention is not a parity bar here
+    assert rel.mean() < 0.08 and np.quantile(rel, 0.95) < 0.25
