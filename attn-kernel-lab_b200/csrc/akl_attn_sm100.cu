@@ -1,6 +1,6 @@
 // Fused FP8 paged-prefill attention for sm_100a: tcgen05 kind::f8f6f4 MMAs with the S and O
 // accumulators in tensor memory, operand tiles brought in by bulk asynchronous copies,
-// exact online softmax (P x 448 fold, exact rescale skip) on a softmax warpgroup.
+// exact online softmax (P x 448 fold, exact rescale skip) on two softmax warpgroups.
 //
 // It computes what the reference's mma.sync kernel computes
 // (src/attn_kernel_lab/csrc/fp8_prefill_attn.cu:220-681): per (128-row Q tile, q head)
@@ -15,10 +15,17 @@
 // per 64-key tile, in tile order -- the tile sequence is part of the operator because P is
 // rounded against the running maximum.
 //
-// CTA = 6 warps:  warps 0-3  softmax / O-rescale / epilogue (thread i owns query row i, which
-//                            is TMEM lane i),
-//                 warp 4     lane 0 issues the bulk copies; the warp owns TMEM alloc/free,
-//                 warp 5     lane 0 issues every tcgen05.mma.
+// CTA = 10 warps:
+//   warps 0-3  softmax warpgroup 0: even 64-key tiles  } thread i of either group owns query
+//   warps 4-7  softmax warpgroup 1: odd  64-key tiles  } row i, which is TMEM lane i
+//   warp  8    lane 0 issues the bulk copies; the warp owns TMEM allocation,
+//   warp  9    lane 0 issues every tcgen05.mma.
+// The two groups alternate tiles so that two warps share each scheduler and hide each other's
+// latencies; the running row maximum is the only state that must travel from one tile to the
+// next, and it is handed from group to group through a 64-bit (sequence, value) word per row in
+// shared memory.  Each group keeps its own partial l against its own last maximum; the two
+// are combined once, in the epilogue.
+//
 // Shared memory: Q tile 32 KiB; K and V^T 128-key pair tiles, two stages each (2 x 64 KiB);
 // P 2 x 16 KiB.  Tensor memory (512 columns): O = columns 0-255, S ping-pong = 256-383 /
 // 384-511.  QK^T runs at N = 128 keys per MMA group, softmax and PV at the operator's 64-key
@@ -34,14 +41,17 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = 32768;
 constexpr uint32_t kOffV = kOffK + 2 * 32768;
 constexpr uint32_t kOffP = kOffV + 2 * 32768;
 constexpr uint32_t kOffBar = kOffP + 2 * 16384;      // 196608
-constexpr uint32_t kOffVmean = kOffBar + 256;
-constexpr uint32_t kSmemBytes = kOffVmean + 1024 + 1024;  // + alignment slack
+constexpr uint32_t kOffVmean = kOffBar + 256;        // 256 floats
+constexpr uint32_t kOffChain = kOffVmean + 1024;     // 128 x u64 running-max hand-off words
+constexpr uint32_t kOffFin = kOffChain + 1024;       // [2][128] (m, l) pairs for the epilogue
+constexpr uint32_t kSmemBytes = kOffFin + 2048 + 1024;   // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256;
 constexpr uint32_t kIdescQK = idesc_e4m3(128, 128);
@@ -53,15 +63,16 @@ constexpr long long kWaitCycles = 4000000000ll;      // ~2 s: a wait that long i
 // barrier slots (8 bytes each)
 enum {
   B_QFULL = 0,
-  B_KFULL = 1,   // [2]
-  B_KEMPTY = 3,  // [2]
-  B_VFULL = 5,   // [2]
-  B_VEMPTY = 7,  // [2]
-  B_SFULL = 9,   // [2]
-  B_SEMPTY = 11, // [2]
-  B_PFULL = 13,  // [2][2]
-  B_PVDONE = 17,
-  B_COUNT = 18
+  B_KFULL = 1,    // [2]
+  B_KEMPTY = 3,   // [2]
+  B_VFULL = 5,    // [2]
+  B_VEMPTY = 7,   // [2]
+  B_SFULL = 9,    // [2]
+  B_SEMPTY = 11,  // [2]
+  B_PFULL = 13,   // [2][2]
+  B_PVDONE = 17,  // [2]: PV of even tiles / of odd tiles
+  B_ALLDONE = 19,
+  B_COUNT = 20
 };
 
 struct Ctx {
@@ -70,22 +81,48 @@ struct Ctx {
   volatile int* abort_flag;   // shared memory
 };
 
+__device__ __forceinline__ bool give_up(const Ctx& c, long long& t0) {
+  if (t0 == 0) {
+    t0 = clock64();
+    return false;
+  }
+  if (*c.abort_flag || clock64() - t0 > kWaitCycles) {
+    *c.abort_flag = 1;
+    atomicCAS(c.status, 0, AKL_ERR_TIMEOUT);
+    return true;
+  }
+  return false;
+}
+
 // Bounded mbarrier wait.  Returns false after ~2 s (or as soon as another thread of the CTA
 // gave up), having recorded AKL_ERR_TIMEOUT in the status word.
+//
+// A parity wait is only meaningful while the waiter is at most one phase behind the barrier,
+// so every waiter in this kernel observes every phase of the barriers it waits on, in order.
 __device__ __forceinline__ bool wait(const Ctx& c, int slot, uint32_t parity) {
   const uint32_t bar = c.bars + slot * 8;
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0xFFFu) == 0) {
-      if (t0 == 0) {
-        t0 = clock64();
-      } else if (*c.abort_flag || clock64() - t0 > kWaitCycles) {
-        *c.abort_flag = 1;
-        atomicCAS(c.status, 0, AKL_ERR_TIMEOUT);
-        return false;
-      }
+    if ((spin & 0xFFFu) == 0 && give_up(c, t0)) return false;
+  }
+}
+
+// Running-maximum hand-off: word = (tiles finished << 32) | float bits of the maximum after
+// them.  The consumer of tile j waits until `tiles finished` reaches j.
+__device__ __forceinline__ void chain_post(uint32_t addr, uint32_t seq, float m) {
+  asm volatile("st.volatile.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(__float_as_uint(m)), "r"(seq) : "memory");
+}
+__device__ __forceinline__ bool chain_wait(const Ctx& c, uint32_t addr, uint32_t seq, float& m) {
+  long long t0 = 0;
+  for (uint32_t spin = 1;; ++spin) {
+    uint32_t lo, hi;
+    asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(addr) : "memory");
+    if (hi == seq) {
+      m = __uint_as_float(lo);
+      return true;
     }
+    if ((spin & 0xFFFu) == 0 && give_up(c, t0)) return false;
   }
 }
 
@@ -114,6 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
   float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
+  float2* sm_fin = reinterpret_cast<float2*>(smem_gen + kOffFin);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
   const int h = blockIdx.y;
@@ -138,24 +176,26 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       mbar_init(b + (B_VFULL + i) * 8, 1);
       mbar_init(b + (B_VEMPTY + i) * 8, 1);
       mbar_init(b + (B_SFULL + i) * 8, 1);
-      mbar_init(b + (B_SEMPTY + i) * 8, 128);
+      mbar_init(b + (B_SEMPTY + i) * 8, 256);
+      mbar_init(b + (B_PVDONE + i) * 8, 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(b + (B_PFULL + i) * 8, 128);
-    mbar_init(b + B_PVDONE * 8, 1);
+    mbar_init(b + B_ALLDONE * 8, 1);
     mbar_init_fence();
     fence_async_smem();
   }
-  if (warp == 4) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  if (warp == kProducerWarp) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
   if (tid < 128) {
     sm_vmean[tid] = g.vmean[kvh * kD + tid];
     sm_vmean[tid + 128] = g.vmean[kvh * kD + tid + 128];
+    chain_post(smem + kOffChain + tid * 8, 0u, -INFINITY);      // "zero tiles finished, max = -inf"
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0 && ntile > 0) {
       const uint8_t* qsrc = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + qt) * kImageBytes;
@@ -175,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
                  ctx.bars + (B_VFULL + s) * 8);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && ntile > 0) {
       bool ok = wait(ctx, B_QFULL, 0) && wait(ctx, B_KFULL + 0, 0);
@@ -205,31 +245,46 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
           if (!ok) break;
           tc_fence_after();
           issue_pv(smem, tmem + kColO, b, c, j > 0);
-          tc_commit(ctx.bars + B_PVDONE * 8);
+          tc_commit(ctx.bars + (B_PVDONE + c) * 8);
         }
         if (ok) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
       }
+      if (ok) tc_commit(ctx.bars + B_ALLDONE * 8);
     }
   } else {
-    // ------------------------------------------------------------ softmax warpgroup
-    const int row = tid;                      // query row inside the tile == TMEM lane
+    // ------------------------------------------------------------ softmax warpgroups
+    const int wg = warp >> 2;                  // 0: even tiles, 1: odd tiles
+    const int row = tid & 127;                 // query row inside the tile == TMEM lane
     const int grow = m0 + row;
-    const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t chain = smem + kOffChain + row * 8;
     long long lim_ll = static_cast<long long>(g.prefix) + grow - g.kv_pos0;
     const int limit = static_cast<int>(lim_ll > g.N - 1 ? g.N - 1 : lim_ll);   // last visible local key (may be < 0)
     const float qs = g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
     const float* kscale = g.kscale + kvh * g.ntiles_cap;
     const float* vlog2r = g.vlog2r + kvh * g.ntiles_cap;
     const float* vinvr = g.vinvr + kvh * g.ntiles_cap;
-    float m = -INFINITY, l = 0.f;
+    float m_own = -INFINITY, l_own = 0.f;      // this group's partial (m, l)
     bool ok = true;
 
-    for (int j = 0; j < ntile; ++j) {
-      const int u = j >> 1, c = j & 1, b = u & 1;
-      if (c == 0) {
-        if (!wait(ctx, B_SFULL + b, (u >> 1) & 1)) { ok = false; break; }
-        tc_fence_after();
+    // per-tile constants are fetched one tile ahead so their latency is off the critical path
+    float c_ks = 0.f, c_l2r = 0.f, c_inv = 0.f;
+    if (wg < ntile) {
+      c_ks = __ldg(kscale + wg);
+      c_l2r = __ldg(vlog2r + wg);
+      c_inv = __ldg(vinvr + wg);
+    }
+
+    for (int j = wg; j < ntile; j += 2) {
+      const int u = j >> 1, b = u & 1, c = wg;
+      const float t_ks = c_ks, t_l2r = c_l2r, t_inv = c_inv;
+      if (j + 2 < ntile) {
+        c_ks = __ldg(kscale + j + 2);
+        c_l2r = __ldg(vlog2r + j + 2);
+        c_inv = __ldg(vinvr + j + 2);
       }
+      if (!wait(ctx, B_SFULL + b, (u >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
       __syncwarp();
       uint32_t sr[64];
       {
@@ -241,16 +296,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) { sr[i] = lo32[i]; sr[32 + i] = hi32[i]; }
       }
-      if (c == 1 || j == ntile - 1) {
-        tc_fence_before();
-        mbar_arrive(ctx.bars + (B_SEMPTY + b) * 8);
-      }
+      tc_fence_before();
+      mbar_arrive(ctx.bars + (B_SEMPTY + b) * 8);      // 256 arrivals free the S buffer
       if (kDump) {
         float* dst = g.dbg_s + ((((static_cast<size_t>(h) * g.mtiles + qt) * g.nt + j) * kQTile + row) * kTile);
 #pragma unroll
         for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(sr[i]);
       }
-      const float sc = qs * __ldg(kscale + j);
+      const float sc = qs * t_ks;
       const int rem = limit - j * kTile;
       float s[64];
       float rowmax = -INFINITY;
@@ -268,26 +321,29 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
           rowmax = fmaxf(rowmax, s[i]);
         }
       }
-      const float m_new = fmaxf(m, rowmax);
-      const float alpha = (m == -INFINITY) ? 0.f : ex2((m - m_new) * kLog2e);
-      const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + __ldg(vlog2r + j)) - m_new * kLog2e;
-      m = m_new;
+      // running maximum: take the value after tile j-1 from the other group, publish ours
+      float m_prev;
+      if (!chain_wait(ctx, chain, static_cast<uint32_t>(j), m_prev)) { ok = false; break; }
+      const float m_new = fmaxf(m_prev, rowmax);
+      chain_post(chain, static_cast<uint32_t>(j + 1), m_new);
+      const float alpha_o = (m_prev == -INFINITY) ? 0.f : ex2((m_prev - m_new) * kLog2e);
+      const float alpha_l = (m_own == -INFINITY) ? 0.f : ex2((m_own - m_new) * kLog2e);
+      const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
+      m_own = m_new;
       float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
         s[i] = ex2(fmaf(s[i], kLog2e, pc));
         part[i & 3] += s[i];
       }
-      l = l * alpha + ((part[0] + part[1]) + (part[2] + part[3])) * __ldg(vinvr + j);
+      l_own = l_own * alpha_l + ((part[0] + part[1]) + (part[2] + part[3])) * t_inv;
 
-      // Every thread observes every phase of the PV-done barrier, in order: a parity wait
-      // is only meaningful while the waiter is at most one phase behind, and a thread that
-      // skipped phases (no rescale for a few tiles) could otherwise see a stale parity as
-      // "done" and rescale O under a running MMA.
-      if (j > 0 && !wait(ctx, B_PVDONE, (j - 1) & 1)) { ok = false; break; }
+      // O may be touched only after the PV of tile j-1 has completed.  That PV commits to the
+      // other parity's barrier, whose phases this group observes one by one.
+      if (j > 0 && !wait(ctx, B_PVDONE + (1 - c), ((j - 1) >> 1) & 1)) { ok = false; break; }
       // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
       __syncwarp();
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (j > 0 && __any_sync(0xffffffffu, alpha_o != 1.f)) {
         tc_fence_after();
 #pragma unroll 1
         for (int ch = 0; ch < 8; ++ch) {
@@ -295,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
           tmem_ld32(lane_base + kColO + ch * 32, o);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_o);
           tmem_st32(lane_base + kColO + ch * 32, o);
         }
         tmem_wait_st();
@@ -322,14 +378,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
     }
 
     // ---------------------------------------------------------- epilogue
-    if (ok && ntile > 0) ok = wait(ctx, B_PVDONE, (ntile - 1) & 1);
-    ok = __all_sync(0xffffffffu, ok);
+    // combine the two groups' partial (m, l); then each group writes half of the channels
+    sm_fin[wg * 128 + row] = make_float2(m_own, l_own);
+    if (ok && ntile > 0) ok = wait(ctx, B_ALLDONE, 0);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    ok = __all_sync(0xffffffffu, ok) && (abort_flag == 0);
     if (ok) {
       tc_fence_after();
+      const float2 f0 = sm_fin[row], f1 = sm_fin[128 + row];
+      const float m = fmaxf(f0.x, f1.x);
+      const float l = ((f0.x == -INFINITY) ? 0.f : f0.y * ex2((f0.x - m) * kLog2e)) +
+                      ((f1.x == -INFINITY) ? 0.f : f1.y * ex2((f1.x - m) * kLog2e));
       const float inv_l = (l > 0.f) ? g.vscale[kvh] / l : 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(g.out) + (static_cast<size_t>(grow) * g.Hq + h) * kD;
 #pragma unroll 1
-      for (int ch = 0; ch < 8; ++ch) {
+      for (int chh = 0; chh < 4; ++chh) {
+        const int ch = wg * 4 + chh;
         uint32_t o[32];
         if (ntile > 0) {
           tmem_ld32(lane_base + kColO + ch * 32, o);
@@ -354,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
           }
         }
       }
-      if (g.lse_out != nullptr && grow < g.T) {
+      if (wg == 0 && g.lse_out != nullptr && grow < g.T) {
         g.lse_out[static_cast<size_t>(grow) * g.Hq + h] =
             (l > 0.f) ? fmaf(m, kLog2e, log2f(l) - kLog2_448) : -INFINITY;
       }
@@ -363,7 +427,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
   }
 
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
