@@ -41,6 +41,18 @@ namespace {
 
 using namespace ptx;
 
+// Timeline probe for kernel development: compiled in only with -DAKL_TRACE, never in the
+// shipped library.  Thread 0 of each softmax group stamps clock64() at fixed points of a tile.
+#ifdef AKL_TRACE
+#define AKL_TRACE_POINT(k)                                                                       \
+  do {                                                                                           \
+    if (g.dbg_s != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && j < 512)         \
+      reinterpret_cast<long long*>(g.dbg_s)[(j * 8 + (k))] = clock64();                          \
+  } while (0)
+#else
+#define AKL_TRACE_POINT(k) do { } while (0)
+#endif
+
 constexpr int kThreads = 320;
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
 constexpr uint32_t kOffQ = 0;
@@ -283,6 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
         c_l2r = __ldg(vlog2r + j + 2);
         c_inv = __ldg(vinvr + j + 2);
       }
+      AKL_TRACE_POINT(7);
       if (!wait(ctx, B_SFULL + b, (u >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       __syncwarp();
@@ -296,6 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) { sr[i] = lo32[i]; sr[32 + i] = hi32[i]; }
       }
+      AKL_TRACE_POINT(0);
       tc_fence_before();
       mbar_arrive(ctx.bars + (B_SEMPTY + b) * 8);      // 256 arrivals free the S buffer
       if (kDump) {
@@ -306,26 +320,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       const float sc = qs * t_ks;
       const int rem = limit - j * kTile;
       float s[64];
-      float rowmax = -INFINITY;
+      float rmax[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) rmax[i] = -INFINITY;
       if (rem >= kTile - 1) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           s[i] = __uint_as_float(sr[i]) * sc;
-          rowmax = fmaxf(rowmax, s[i]);
+          rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
         }
       } else {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float v = __uint_as_float(sr[i]) * sc;
           s[i] = (i <= rem) ? v : -INFINITY;
-          rowmax = fmaxf(rowmax, s[i]);
+          rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
         }
       }
+      const float rowmax = fmaxf(fmaxf(fmaxf(rmax[0], rmax[1]), fmaxf(rmax[2], rmax[3])),
+                                 fmaxf(fmaxf(rmax[4], rmax[5]), fmaxf(rmax[6], rmax[7])));
+      AKL_TRACE_POINT(1);
       // running maximum: take the value after tile j-1 from the other group, publish ours
       float m_prev;
       if (!chain_wait(ctx, chain, static_cast<uint32_t>(j), m_prev)) { ok = false; break; }
       const float m_new = fmaxf(m_prev, rowmax);
       chain_post(chain, static_cast<uint32_t>(j + 1), m_new);
+      AKL_TRACE_POINT(2);
       const float alpha_o = (m_prev == -INFINITY) ? 0.f : ex2((m_prev - m_new) * kLog2e);
       const float alpha_l = (m_own == -INFINITY) ? 0.f : ex2((m_own - m_new) * kLog2e);
       const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
@@ -338,26 +358,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       }
       l_own = l_own * alpha_l + ((part[0] + part[1]) + (part[2] + part[3])) * t_inv;
 
-      // O may be touched only after the PV of tile j-1 has completed.  That PV commits to the
-      // other parity's barrier, whose phases this group observes one by one.
-      if (j > 0 && !wait(ctx, B_PVDONE + (1 - c), ((j - 1) >> 1) & 1)) { ok = false; break; }
-      // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
-      __syncwarp();
-      if (j > 0 && __any_sync(0xffffffffu, alpha_o != 1.f)) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t o[32];
-          tmem_ld32(lane_base + kColO + ch * 32, o);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha_o);
-          tmem_st32(lane_base + kColO + ch * 32, o);
-        }
-        tmem_wait_st();
-      }
-
-      // P -> E4M3 -> shared memory (128-byte-swizzled A operand of the PV MMA)
+      AKL_TRACE_POINT(3);
+      // P -> E4M3 -> shared memory (128-byte-swizzled A operand of the PV MMA).  Written before
+      // the wait below: the slot is free (its previous PV precedes this pair's QK^T, whose
+      // completion this thread has already observed), and the 64 score registers die here.
       const uint32_t prow = smem + kOffP + b * 16384;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -373,8 +377,35 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
         }
       }
       fence_async_smem();
+      AKL_TRACE_POINT(4);
+
+      // O may be touched only after the PV of tile j-1 has completed.  That PV commits to the
+      // other parity's barrier, whose phases this group observes one by one.
+      if (j > 0 && !wait(ctx, B_PVDONE + (1 - c), ((j - 1) >> 1) & 1)) { ok = false; break; }
+      AKL_TRACE_POINT(5);
+      // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
+      __syncwarp();
+      if (j > 0 && __any_sync(0xffffffffu, alpha_o != 1.f)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int ch = 0; ch < 8; ch += 2) {
+          uint32_t oa[32], ob[32];
+          tmem_ld32(lane_base + kColO + ch * 32, oa);
+          tmem_ld32(lane_base + kColO + ch * 32 + 32, ob);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            oa[i] = __float_as_uint(__uint_as_float(oa[i]) * alpha_o);
+            ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha_o);
+          }
+          tmem_st32(lane_base + kColO + ch * 32, oa);
+          tmem_st32(lane_base + kColO + ch * 32 + 32, ob);
+        }
+        tmem_wait_st();
+      }
       tc_fence_before();
       mbar_arrive(ctx.bars + (B_PFULL + b * 2 + c) * 8);
+      AKL_TRACE_POINT(6);
     }
 
     // ---------------------------------------------------------- epilogue
@@ -449,8 +480,13 @@ int launch_attention(const Geom& g, cudaStream_t s, bool dump) {
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   dim3 grid(g.mtiles, g.Hq);
+#ifdef AKL_TRACE
+  if (dump)   // development build: the dump pointer receives the timeline, not the scores
+    attn_sm100_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(g);
+#else
   if (dump)
     attn_sm100_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(g);
+#endif
   else
     attn_sm100_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(g);
   e = cudaGetLastError();
