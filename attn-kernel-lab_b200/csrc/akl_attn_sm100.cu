@@ -15,11 +15,19 @@
 // per 64-key tile, in tile order -- the tile sequence is part of the operator because P is
 // rounded against the running maximum.
 //
-// CTA = 10 warps:
-//   warps 0-3  softmax warpgroup 0: even 64-key tiles  } thread i of either group owns query
-//   warps 4-7  softmax warpgroup 1: odd  64-key tiles  } row i, which is TMEM lane i
-//   warp  8    lane 0 issues the bulk copies; the warp owns TMEM allocation,
-//   warp  9    lane 0 issues every tcgen05.mma.
+// CTA = 16 warps:
+//   warps 0-3   softmax warpgroup 0: even 64-key tiles  } thread i of a group owns query row i,
+//   warps 4-7   softmax warpgroup 1: odd  64-key tiles  } which is TMEM lane i
+//   warps 8-11  correction warpgroup: multiplies O by alpha between two PV MMAs when a row's
+//               running maximum moved, so the softmax groups never wait for the tensor pipe,
+//   warp  12    lane 0 issues the Q and K bulk copies; the warp owns TMEM allocation,
+//   warp  14    lane 0 issues the V^T bulk copies (its own thread, so that a K tile whose stage
+//               is free is never queued behind a wait for a V stage),
+//   warp  13    lane 0 issues the PV MMAs (after P(j) is written and O carries alpha_j),
+//   warp  15    lane 0 issues the QK^T MMAs (as soon as an S buffer has been read out).
+// The two issuing threads sit on different warp schedulers and never wait for each other's
+// inputs, so the tensor pipe always has the QK^T of a later pair to run while the correction of
+// the next tile is in flight.
 // The two groups alternate tiles so that two warps share each scheduler and hide each other's
 // latencies; the running row maximum is the only state that must travel from one tile to the
 // next, and it is handed from group to group through a 64-bit (sequence, value) word per row in
@@ -49,12 +57,18 @@ using namespace ptx;
     if (g.dbg_s != nullptr && row == 0 && blockIdx.x == 0 && blockIdx.y == 0 && j < 512)         \
       reinterpret_cast<long long*>(g.dbg_s)[(j * 8 + (k))] = clock64();                          \
   } while (0)
+#define AKL_TRACE_AUX(cond, j_, k)                                                                \
+  do {                                                                                           \
+    if (g.dbg_s != nullptr && (cond) && blockIdx.x == 0 && blockIdx.y == 0 && (j_) < 512)        \
+      reinterpret_cast<long long*>(g.dbg_s)[4096 + ((j_) * 8 + (k))] = clock64();                \
+  } while (0)
 #else
 #define AKL_TRACE_POINT(k) do { } while (0)
+#define AKL_TRACE_AUX(cond, j_, k) do { } while (0)
 #endif
 
-constexpr int kThreads = 320;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 512;
+constexpr int kProducerWarp = 12, kPvWarp = 13, kVProducerWarp = 14, kQkWarp = 15;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = 32768;
 constexpr uint32_t kOffV = kOffK + 2 * 32768;
@@ -63,7 +77,8 @@ constexpr uint32_t kOffBar = kOffP + 2 * 16384;      // 196608
 constexpr uint32_t kOffVmean = kOffBar + 256;        // 256 floats
 constexpr uint32_t kOffChain = kOffVmean + 1024;     // 128 x u64 running-max hand-off words
 constexpr uint32_t kOffFin = kOffChain + 1024;       // [2][128] (m, l) pairs for the epilogue
-constexpr uint32_t kSmemBytes = kOffFin + 2048 + 1024;   // + alignment slack
+constexpr uint32_t kOffAlpha = kOffFin + 2048;       // [4][128] floats: alpha of tile j in slot j & 3
+constexpr uint32_t kSmemBytes = kOffAlpha + 2048 + 1024;   // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256;
 constexpr uint32_t kIdescQK = idesc_e4m3(128, 128);
@@ -82,9 +97,12 @@ enum {
   B_SFULL = 9,    // [2]
   B_SEMPTY = 11,  // [2]
   B_PFULL = 13,   // [2][2]
-  B_PVDONE = 17,  // [2]: PV of even tiles / of odd tiles
-  B_ALLDONE = 19,
-  B_COUNT = 20
+  B_PVDONE = 17,  // one phase per tile; only the correction group waits on it, every tile
+  B_ALLDONE = 18,
+  B_AREADY = 19,  // [4] alpha of tile j published (slot j & 3)
+  B_OREADY = 23,  // O carries alpha_j: PV(j) may be issued
+  B_PEMPTY = 24,  // [2][2] PV(j) has read P slot (j>>1)&1, j&1 (and the correction of tile j is over)
+  B_COUNT = 28
 };
 
 struct Ctx {
@@ -138,21 +156,27 @@ __device__ __forceinline__ bool chain_wait(const Ctx& c, uint32_t addr, uint32_t
   }
 }
 
-__device__ __forceinline__ void issue_qk(uint32_t smem, uint32_t tmem_s, int stage) {
-  const uint32_t qa = smem + kOffQ, kb = smem + kOffK + stage * 32768;
+// Descriptor of a K-major SWIZZLE_128B operand: the high word is constant, the low word is the
+// 16-byte-unit address (plus the unused leading-offset field); a byte offset adds offset/16.
+constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_off) {
+  return (static_cast<uint64_t>(kDescHi) << 32) | (lo + (byte_off >> 4));
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+
+// QK^T of one 128-key pair: 8 MMAs of K = 32 (two 128-byte planes x four 32-byte steps).
+__device__ __forceinline__ void issue_qk(uint32_t q_lo, uint32_t k_lo, uint32_t tmem_s) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t off = (k >> 2) * kPlaneBytes + (k & 3) * 32;
-    mma_f8_ss(tmem_s, smem_desc_k128(qa + off), smem_desc_k128(kb + off), kIdescQK, k > 0);
+    mma_f8_ss(tmem_s, desc_at(q_lo, off), desc_at(k_lo, off), kIdescQK, k > 0 ? 1u : 0u);
   }
 }
 
-__device__ __forceinline__ void issue_pv(uint32_t smem, uint32_t tmem_o, int buf, int half, bool accumulate) {
-  const uint32_t pa = smem + kOffP + buf * 16384 + half * 64;
-  const uint32_t vb = smem + kOffV + buf * 32768 + half * 64;
-#pragma unroll
-  for (int k = 0; k < 2; ++k)
-    mma_f8_ss(tmem_o, smem_desc_k128(pa + k * 32), smem_desc_k128(vb + k * 32), kIdescPV, (accumulate || k > 0) ? 1u : 0u);
+// PV of one 64-key tile: 2 MMAs of K = 32 inside one 128-byte row (offset half*64).
+__device__ __forceinline__ void issue_pv(uint32_t p_lo, uint32_t v_lo, uint32_t tmem_o, uint32_t accumulate) {
+  mma_f8_ss(tmem_o, desc_at(p_lo, 0), desc_at(v_lo, 0), kIdescPV, accumulate);
+  mma_f8_ss(tmem_o, desc_at(p_lo, 32), desc_at(v_lo, 32), kIdescPV, 1u);
 }
 
 template <bool kDump>
@@ -189,9 +213,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       mbar_init(b + (B_VEMPTY + i) * 8, 1);
       mbar_init(b + (B_SFULL + i) * 8, 1);
       mbar_init(b + (B_SEMPTY + i) * 8, 256);
-      mbar_init(b + (B_PVDONE + i) * 8, 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(b + (B_PFULL + i) * 8, 128);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(b + (B_PFULL + i) * 8, 128);
+      mbar_init(b + (B_AREADY + i) * 8, 128);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(b + (B_PEMPTY + i) * 8, 1);
+    mbar_init(b + B_PVDONE * 8, 1);
+    mbar_init(b + B_OREADY * 8, 128);
     mbar_init(b + B_ALLDONE * 8, 1);
     mbar_init_fence();
     fence_async_smem();
@@ -212,7 +241,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
     if (lane == 0 && ntile > 0) {
       const uint8_t* qsrc = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + qt) * kImageBytes;
       const uint8_t* ksrc = g.k8 + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
-      const uint8_t* vsrc = g.v8t + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
       mbar_expect_tx(ctx.bars + B_QFULL * 8, kImageBytes);
       bulk_g2s(smem + kOffQ, qsrc, kImageBytes, ctx.bars + B_QFULL * 8);
       for (int u = 0; u < npair; ++u) {
@@ -221,47 +249,91 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
         mbar_expect_tx(ctx.bars + (B_KFULL + s) * 8, kImageBytes);
         bulk_g2s(smem + kOffK + s * 32768, ksrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
                  ctx.bars + (B_KFULL + s) * 8);
+      }
+    }
+  } else if (warp == kVProducerWarp) {
+    if (lane == 0 && ntile > 0) {
+      const uint8_t* vsrc = g.v8t + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
+      for (int u = 0; u < npair; ++u) {
+        const int s = u & 1, n = u >> 1;
         if (n >= 1 && !wait(ctx, B_VEMPTY + s, (n - 1) & 1)) break;
         mbar_expect_tx(ctx.bars + (B_VFULL + s) * 8, kImageBytes);
         bulk_g2s(smem + kOffV + s * 32768, vsrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
                  ctx.bars + (B_VFULL + s) * 8);
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == kQkWarp) {
+    // ------------------------------------------------------------ QK^T issuer
     if (lane == 0 && ntile > 0) {
-      bool ok = wait(ctx, B_QFULL, 0) && wait(ctx, B_KFULL + 0, 0);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(smem, tmem + kColS, 0);
-        tc_commit(ctx.bars + (B_SFULL + 0) * 8);
-        tc_commit(ctx.bars + (B_KEMPTY + 0) * 8);
-      }
+      const uint32_t q_lo = desc_lo(smem + kOffQ);
+      bool ok = wait(ctx, B_QFULL, 0);
       for (int u = 0; ok && u < npair; ++u) {
-        if (u + 1 < npair) {
-          const int s = (u + 1) & 1, n = (u + 1) >> 1;
-          ok = wait(ctx, B_KFULL + s, n & 1);
-          if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + s, (n - 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          issue_qk(smem, tmem + kColS + s * 128, s);
-          tc_commit(ctx.bars + (B_SFULL + s) * 8);
-          tc_commit(ctx.bars + (B_KEMPTY + s) * 8);
-        }
-        const int b = u & 1, par = (u >> 1) & 1;
-        ok = wait(ctx, B_VFULL + b, par);
-        for (int c = 0; ok && c < 2; ++c) {
-          const int j = 2 * u + c;
-          if (j >= ntile) break;
-          ok = wait(ctx, B_PFULL + b * 2 + c, par);
-          if (!ok) break;
-          tc_fence_after();
-          issue_pv(smem, tmem + kColO, b, c, j > 0);
-          tc_commit(ctx.bars + (B_PVDONE + c) * 8);
-        }
-        if (ok) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
+        const int b = u & 1, n = u >> 1;
+        ok = wait(ctx, B_KFULL + b, n & 1);
+        if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + b, (n - 1) & 1);   // both groups have read S(u-2)
+        if (!ok) break;
+        tc_fence_after();
+        issue_qk(q_lo, desc_lo(smem + kOffK + b * 32768), tmem + kColS + b * 128);
+        tc_commit(ctx.bars + (B_SFULL + b) * 8);
+        tc_commit(ctx.bars + (B_KEMPTY + b) * 8);
+      }
+    }
+  } else if (warp == kPvWarp) {
+    // ------------------------------------------------------------ PV issuer
+    if (lane == 0 && ntile > 0) {
+      bool ok = true;
+      for (int j = 0; ok && j < ntile; ++j) {
+        const int u = j >> 1, c = j & 1, b = u & 1, par = (u >> 1) & 1;
+        if (c == 0) ok = wait(ctx, B_VFULL + b, par);
+        ok = ok && wait(ctx, B_PFULL + b * 2 + c, par) && wait(ctx, B_OREADY, j & 1);
+        if (!ok) break;
+        tc_fence_after();
+        AKL_TRACE_AUX(true, j, 3);
+        issue_pv(desc_lo(smem + kOffP + b * 16384 + c * 64), desc_lo(smem + kOffV + b * 32768 + c * 64),
+                 tmem + kColO, j > 0 ? 1u : 0u);
+        tc_commit(ctx.bars + B_PVDONE * 8);
+        tc_commit(ctx.bars + (B_PEMPTY + b * 2 + c) * 8);
+        AKL_TRACE_AUX(true, j, 4);
+        if (c == 1 || j == ntile - 1) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
       }
       if (ok) tc_commit(ctx.bars + B_ALLDONE * 8);
+    }
+  } else if (warp >= 8 && warp < 12) {
+    // ------------------------------------------------------------ correction warpgroup
+    const int row = tid & 127;
+    const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const float* sm_alpha = reinterpret_cast<const float*>(smem_gen + kOffAlpha);
+    for (int j = 0; j < ntile; ++j) {
+      if (!wait(ctx, B_AREADY + (j & 3), (j >> 2) & 1)) break;
+      AKL_TRACE_AUX(row == 0, j, 0);
+      const float alpha = sm_alpha[(j & 3) * 128 + row];
+      if (j > 0) {
+        if (!wait(ctx, B_PVDONE, (j - 1) & 1)) break;          // every phase, in order
+        AKL_TRACE_AUX(row == 0, j, 1);
+        __syncwarp();
+        // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int ch = 0; ch < 8; ch += 2) {
+            uint32_t oa[32], ob[32];
+            tmem_ld32(lane_base + kColO + ch * 32, oa);
+            tmem_ld32(lane_base + kColO + ch * 32 + 32, ob);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              oa[i] = __float_as_uint(__uint_as_float(oa[i]) * alpha);
+              ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
+            }
+            tmem_st32(lane_base + kColO + ch * 32, oa);
+            tmem_st32(lane_base + kColO + ch * 32 + 32, ob);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+      }
+      mbar_arrive(ctx.bars + B_OREADY * 8);
+      AKL_TRACE_AUX(row == 0, j, 2);
     }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
@@ -270,6 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
     const int grow = m0 + row;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t chain = smem + kOffChain + row * 8;
+    float* sm_alpha = reinterpret_cast<float*>(smem_gen + kOffAlpha);
     long long lim_ll = static_cast<long long>(g.prefix) + grow - g.kv_pos0;
     const int limit = static_cast<int>(lim_ll > g.N - 1 ? g.N - 1 : lim_ll);   // last visible local key (may be < 0)
     const float qs = g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
@@ -296,6 +369,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
         c_inv = __ldg(vinvr + j + 2);
       }
       AKL_TRACE_POINT(7);
+      // tile j reuses the P slot and the alpha slot of tile j-4: its PV must have completed
+      // (which also means the correction group is done with alpha(j-4))
+      if (j >= 4 && !wait(ctx, B_PEMPTY + b * 2 + c, ((u >> 1) - 1) & 1)) { ok = false; break; }
       if (!wait(ctx, B_SFULL + b, (u >> 1) & 1)) { ok = false; break; }
       tc_fence_after();
       __syncwarp();
@@ -346,7 +422,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       const float m_new = fmaxf(m_prev, rowmax);
       chain_post(chain, static_cast<uint32_t>(j + 1), m_new);
       AKL_TRACE_POINT(2);
+      // alpha of this tile goes to the correction group
       const float alpha_o = (m_prev == -INFINITY) ? 0.f : ex2((m_prev - m_new) * kLog2e);
+      sm_alpha[(j & 3) * 128 + row] = alpha_o;
+      mbar_arrive(ctx.bars + (B_AREADY + (j & 3)) * 8);
       const float alpha_l = (m_own == -INFINITY) ? 0.f : ex2((m_own - m_new) * kLog2e);
       const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
       m_own = m_new;
@@ -359,9 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       l_own = l_own * alpha_l + ((part[0] + part[1]) + (part[2] + part[3])) * t_inv;
 
       AKL_TRACE_POINT(3);
-      // P -> E4M3 -> shared memory (128-byte-swizzled A operand of the PV MMA).  Written before
-      // the wait below: the slot is free (its previous PV precedes this pair's QK^T, whose
-      // completion this thread has already observed), and the 64 score registers die here.
+      // P -> E4M3 -> shared memory (128-byte-swizzled A operand of the PV MMA)
       const uint32_t prow = smem + kOffP + b * 16384;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -379,31 +456,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       fence_async_smem();
       AKL_TRACE_POINT(4);
 
-      // O may be touched only after the PV of tile j-1 has completed.  That PV commits to the
-      // other parity's barrier, whose phases this group observes one by one.
-      if (j > 0 && !wait(ctx, B_PVDONE + (1 - c), ((j - 1) >> 1) & 1)) { ok = false; break; }
-      AKL_TRACE_POINT(5);
-      // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
-      __syncwarp();
-      if (j > 0 && __any_sync(0xffffffffu, alpha_o != 1.f)) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int ch = 0; ch < 8; ch += 2) {
-          uint32_t oa[32], ob[32];
-          tmem_ld32(lane_base + kColO + ch * 32, oa);
-          tmem_ld32(lane_base + kColO + ch * 32 + 32, ob);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            oa[i] = __float_as_uint(__uint_as_float(oa[i]) * alpha_o);
-            ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha_o);
-          }
-          tmem_st32(lane_base + kColO + ch * 32, oa);
-          tmem_st32(lane_base + kColO + ch * 32 + 32, ob);
-        }
-        tmem_wait_st();
-      }
-      tc_fence_before();
       mbar_arrive(ctx.bars + (B_PFULL + b * 2 + c) * 8);
       AKL_TRACE_POINT(6);
     }
