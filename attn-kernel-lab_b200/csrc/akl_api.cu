@@ -213,10 +213,8 @@ int akl_prefill_extend(const akl_call_t* c, void* stream) {
     return AKL_ERR_INVALID;   // a split request must make its statistics global between the phases
   if (c->prefix > c->N - c->T) return AKL_ERR_INVALID;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if ((rc = launch_kv_tile_stats(g, c->kv_dtype, c->idx_dtype, s)) != AKL_OK) return rc;
-  if ((rc = launch_quantize_q(g, s)) != AKL_OK) return rc;
-  if ((rc = launch_kv_means(g, s)) != AKL_OK) return rc;
-  if ((rc = launch_kv_scales(g, s)) != AKL_OK) return rc;
+  if ((rc = launch_kv_tile_stats(g, c->kv_dtype, c->idx_dtype, s, /*with_q=*/true)) != AKL_OK) return rc;
+  if ((rc = launch_kv_means(g, s, /*fuse_scales=*/true)) != AKL_OK) return rc;
   if ((rc = launch_kv_transform(g, c->kv_dtype, c->idx_dtype, s)) != AKL_OK) return rc;
   return launch_attention(g, s);
 }

@@ -139,8 +139,8 @@ __device__ __forceinline__ long long load_idx(const void* idx, int i) {
 }
 
 // host-side launchers (one translation unit each)
-int launch_kv_tile_stats(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s);
-int launch_kv_means(const Geom& g, cudaStream_t s);
+int launch_kv_tile_stats(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s, bool with_q = false);
+int launch_kv_means(const Geom& g, cudaStream_t s, bool fuse_scales = false);
 int launch_kv_scales(const Geom& g, cudaStream_t s);
 int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s);
 int launch_quantize_q(const Geom& g, cudaStream_t s);

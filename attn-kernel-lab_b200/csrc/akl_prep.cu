@@ -22,13 +22,22 @@ constexpr int kThreads = 256;
 // 1. per-tile channel sums of K and V, per-tile channel min/max of V
 //    (reference pass 1, quant.py:532-568)
 // ---------------------------------------------------------------------------
-template <int KV_DTYPE, int IDX_DTYPE>
+__device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta);
+
+// Flat grid: CTAs [0, nt*Hkv) take one (tile, kv head) each; with kWithQ the CTAs after them
+// quantise Q rows, so that the two independent passes share one launch and overlap.
+template <int KV_DTYPE, int IDX_DTYPE, bool kWithQ>
 __global__ void __launch_bounds__(kThreads) kv_tile_stats_kernel(Geom g) {
   __shared__ float sm_k[8][kD];
   __shared__ float sm_v[8][kD];
   __shared__ float sm_mx[8][kD];
   __shared__ float sm_mn[8][kD];
-  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int nstat = g.nt * g.Hkv;
+  if (kWithQ && static_cast<int>(blockIdx.x) >= nstat) {
+    quantize_q_rows(g, static_cast<long long>(blockIdx.x) - nstat);
+    return;
+  }
+  const int t = blockIdx.x / g.Hkv, kvh = blockIdx.x % g.Hkv;
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
 
@@ -92,33 +101,64 @@ __global__ void __launch_bounds__(kThreads) kv_tile_stats_kernel(Geom g) {
 // 2. channel means (ordered: tiles inside a 32768-row slab, then slabs) and the
 //    centred per-tile V amax  (quant.py:566-581)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) kv_means_kernel(Geom g) {
+constexpr int kMeansThreads = 1024;
+
+__device__ __forceinline__ void write_tile_scales(const Geom& g, int kvh, int t, float vsm, float floor_) {
+  const int o = kvh * g.ntiles_cap + t;
+  const float vst = __fdiv_rn(fmaxf(g.vam[o], floor_), kFp8Max);
+  float r = __fdiv_rn(__fmul_rn(vst, kFp8Max), vsm);
+  r = fminf(fmaxf(r, 0.0625f), 1.0f);
+  g.vst[o] = vst;
+  g.vlog2r[o] = log2f(r);
+  g.vinvr[o] = __fdiv_rn(1.0f, r);
+}
+
+// One CTA per kv head.  Threads 0-255 add the K tile sums of their channel in tile order inside
+// each 32768-row slab and the slab sums in slab order; threads 256-511 do the same for V (eight
+// loads are kept in flight; the additions stay strictly ordered).  Then 32 warps form the
+// centred per-tile V amax.  With `fuse_scales` (one GPU holds the whole request) the per-tile V
+// scales and fold arrays follow in the same launch.
+template <bool kFuseScales>
+__global__ void __launch_bounds__(kMeansThreads) kv_means_kernel(Geom g) {
   __shared__ float sm_vmean[kD];
-  __shared__ float sm_wmax[8];
-  const int kvh = blockIdx.x, c = threadIdx.x;
+  __shared__ float sm_wmax[32];
+  __shared__ float sm_vsm;
+  const int kvh = blockIdx.x, tid = threadIdx.x;
   const int ntg = g.ntiles_global;
-  float ktot = 0.f, vtot = 0.f;
-  for (int s0 = 0; s0 < ntg; s0 += kSlabTiles) {
-    const int s1 = min(s0 + kSlabTiles, ntg);
-    float kslab = 0.f, vslab = 0.f;
-    for (int t = s0; t < s1; ++t) {
-      kslab = __fadd_rn(kslab, g.ktsum[(static_cast<size_t>(t) * g.Hkv + kvh) * kD + c]);
-      vslab = __fadd_rn(vslab, g.vtsum[(static_cast<size_t>(t) * g.Hkv + kvh) * kD + c]);
+  if (tid < 2 * kD) {
+    const int c = tid & (kD - 1);
+    const bool is_v = tid >= kD;
+    const float* src = (is_v ? g.vtsum : g.ktsum) + static_cast<size_t>(kvh) * kD + c;
+    const size_t stride = static_cast<size_t>(g.Hkv) * kD;
+    float tot = 0.f;
+    for (int s0 = 0; s0 < ntg; s0 += kSlabTiles) {
+      const int s1 = min(s0 + kSlabTiles, ntg);
+      float slab = 0.f;
+      int t = s0;
+      for (; t + 8 <= s1; t += 8) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = src[(t + i) * stride];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) slab = __fadd_rn(slab, x[i]);
+      }
+      for (; t < s1; ++t) slab = __fadd_rn(slab, src[t * stride]);
+      tot = __fadd_rn(tot, slab);
     }
-    ktot = __fadd_rn(ktot, kslab);
-    vtot = __fadd_rn(vtot, vslab);
+    const float denom = static_cast<float>(max(g.n_total, 1));
+    if (is_v) {
+      const float vmean = __fdiv_rn(tot, denom);
+      g.vmean[kvh * kD + c] = vmean;
+      sm_vmean[c] = vmean;
+    } else {
+      g.kmean[kvh * kD + c] = (g.flags & AKL_FLAG_CENTER_K) ? __fdiv_rn(tot, denom) : 0.f;
+    }
   }
-  const float denom = static_cast<float>(max(g.n_total, 1));
-  const float vmean = __fdiv_rn(vtot, denom);
-  const float kmean = (g.flags & AKL_FLAG_CENTER_K) ? __fdiv_rn(ktot, denom) : 0.f;
-  g.kmean[kvh * kD + c] = kmean;
-  g.vmean[kvh * kD + c] = vmean;
-  sm_vmean[c] = vmean;
   __syncthreads();
   // vam[t] = max_c max(fl(mx - mean), fl(mean - mn)); one warp per tile
-  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int w = tid >> 5, lane = tid & 31;
   float wmax = 0.f;
-  for (int t = w; t < g.nt; t += 8) {
+  for (int t = w; t < g.nt; t += kMeansThreads / 32) {
     const float* pmx = g.vtmax + (static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD;
     const float* pmn = g.vtmin + (static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD;
     float a = 0.f;
@@ -134,10 +174,18 @@ __global__ void __launch_bounds__(kThreads) kv_means_kernel(Geom g) {
   }
   if (lane == 0) sm_wmax[w] = wmax;
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     float m = 0.f;
-    for (int i = 0; i < 8; ++i) m = fmaxf(m, sm_wmax[i]);
+    for (int i = 0; i < kMeansThreads / 32; ++i) m = fmaxf(m, sm_wmax[i]);
     g.vsmax[kvh] = m;   // raw, unclamped: a MAX all-reduce may combine ranks here
+    sm_vsm = fmaxf(m, 1e-8f);
+    if (kFuseScales) g.vscale[kvh] = __fdiv_rn(sm_vsm, kFp8Max);
+  }
+  if (kFuseScales) {
+    __syncthreads();       // also orders this CTA's vam stores before the loads below
+    const float vsm = sm_vsm;
+    const float floor_ = __fdiv_rn(vsm, 16.0f);
+    for (int t = tid; t < g.nt; t += kMeansThreads) write_tile_scales(g, kvh, t, vsm, floor_);
   }
 }
 
@@ -148,15 +196,7 @@ __global__ void __launch_bounds__(kThreads) kv_scales_kernel(Geom g) {
   const int kvh = blockIdx.x;
   const float vsm = fmaxf(g.vsmax[kvh], 1e-8f);
   const float floor_ = __fdiv_rn(vsm, 16.0f);
-  for (int t = threadIdx.x; t < g.nt; t += blockDim.x) {
-    const int o = kvh * g.ntiles_cap + t;
-    const float vst = __fdiv_rn(fmaxf(g.vam[o], floor_), kFp8Max);
-    float r = __fdiv_rn(__fmul_rn(vst, kFp8Max), vsm);
-    r = fminf(fmaxf(r, 0.0625f), 1.0f);
-    g.vst[o] = vst;
-    g.vlog2r[o] = log2f(r);
-    g.vinvr[o] = __fdiv_rn(1.0f, r);
-  }
+  for (int t = threadIdx.x; t < g.nt; t += blockDim.x) write_tile_scales(g, kvh, t, vsm, floor_);
   if (threadIdx.x == 0) g.vscale[kvh] = __fdiv_rn(vsm, kFp8Max);
 }
 
@@ -281,37 +321,59 @@ __global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
 // 5. Q: rotate, per-row amax, E4M3, scale*sm_scale  (quant.py:433-480)
 //    one warp per (head, padded row); rows >= T are zero bytes with the clamp scale
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) quantize_q_kernel(Geom g) {
+constexpr int kQRowsPerWarp = 4;
+constexpr int kQRowsPerCta = 8 * kQRowsPerWarp;
+
+// `cta` = index among the Q CTAs; each warp transforms four rows at once (four independent
+// loads, butterflies and divisions in flight).
+__device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mpad = g.mtiles * kQTile;
-  const long long item = static_cast<long long>(blockIdx.x) * 8 + w;
-  if (item >= static_cast<long long>(g.Hq) * mpad) return;
-  const int h = static_cast<int>(item / mpad), r = static_cast<int>(item % mpad);
-  float x[8];
-  float amax = 0.f;
-  if (r < g.T) {
-    const uint16_t* src = reinterpret_cast<const uint16_t*>(g.q) + (static_cast<size_t>(r) * g.Hq + h) * kD + lane * 8;
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
-    unpack8<AKL_KV_BF16>(raw, x);
-    if (g.flags & AKL_FLAG_ROTATE) fwht256(x, lane);
+  const long long item0 = (cta * 8 + w) * kQRowsPerWarp;
+  const long long total = static_cast<long long>(g.Hq) * mpad;
+  float x[kQRowsPerWarp][8];
+  int hh[kQRowsPerWarp], rr[kQRowsPerWarp];
+  uint4 raw[kQRowsPerWarp];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[c]));
-  } else {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) x[c] = 0.f;
+  for (int k = 0; k < kQRowsPerWarp; ++k) {
+    const long long item = item0 + k;
+    hh[k] = static_cast<int>(item / mpad);
+    rr[k] = static_cast<int>(item % mpad);
+    if (item < total && rr[k] < g.T) {
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(g.q) +
+                            (static_cast<size_t>(rr[k]) * g.Hq + hh[k]) * kD + lane * 8;
+      raw[k] = __ldg(reinterpret_cast<const uint4*>(src));
+    }
   }
-  amax = fmaxf(warp_max(amax), 1e-8f);
-  const float scale = __fdiv_rn(amax, kFp8Max);
-  float y[8];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[c], scale);
-  const uint32_t lo = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
-  const uint32_t hi = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
-  const int tile = r >> 7, rr = r & 127, plane = lane >> 4;
-  uint8_t* img = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + tile) * kImageBytes;
-  *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(rr, (lane & 15) * 8)) = make_uint2(lo, hi);
-  if (lane == 0) g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + r] = __fmul_rn(scale, g.sm_scale);
+  for (int k = 0; k < kQRowsPerWarp; ++k) {
+    const long long item = item0 + k;
+    if (item >= total) continue;                       // warp-uniform
+    float amax = 0.f;
+    if (rr[k] < g.T) {
+      unpack8<AKL_KV_BF16>(raw[k], x[k]);
+      if (g.flags & AKL_FLAG_ROTATE) fwht256(x[k], lane);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[k][c]));
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) x[k][c] = 0.f;
+    }
+    amax = fmaxf(warp_max(amax), 1e-8f);
+    const float scale = __fdiv_rn(amax, kFp8Max);
+    float y[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[k][c], scale);
+    const uint32_t lo = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
+    const uint32_t hi = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+    const int tile = rr[k] >> 7, r7 = rr[k] & 127, plane = lane >> 4;
+    uint8_t* img = g.q8 + (static_cast<size_t>(hh[k]) * g.mtiles_cap + tile) * kImageBytes;
+    *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(r7, (lane & 15) * 8)) = make_uint2(lo, hi);
+    if (lane == 0) g.qscale[static_cast<size_t>(hh[k]) * g.mtiles_cap * kQTile + rr[k]] = __fmul_rn(scale, g.sm_scale);
+  }
 }
+
+__global__ void __launch_bounds__(kThreads) quantize_q_kernel(Geom g) { quantize_q_rows(g, blockIdx.x); }
 
 }  // namespace
 
@@ -324,22 +386,38 @@ __global__ void __launch_bounds__(kThreads) quantize_q_kernel(Geom g) {
     }                                              \
   } while (0)
 
-int launch_kv_tile_stats(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s) {
-  dim3 grid(g.nt, g.Hkv);
+static unsigned q_ctas(const Geom& g) {
+  const long long items = static_cast<long long>(g.Hq) * g.mtiles * kQTile;
+  return static_cast<unsigned>((items + kQRowsPerCta - 1) / kQRowsPerCta);
+}
+
+template <bool kWithQ>
+static void launch_stats_impl(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>(g.nt) * g.Hkv + (kWithQ ? q_ctas(g) : 0u);
   if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
-    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I64, kWithQ><<<grid, kThreads, 0, s>>>(g);
   else if (kv_dtype == AKL_KV_BF16)
-    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+    kv_tile_stats_kernel<AKL_KV_BF16, AKL_IDX_I32, kWithQ><<<grid, kThreads, 0, s>>>(g);
   else if (idx_dtype == AKL_IDX_I64)
-    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(g);
+    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I64, kWithQ><<<grid, kThreads, 0, s>>>(g);
   else
-    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
+    kv_tile_stats_kernel<AKL_KV_FP16, AKL_IDX_I32, kWithQ><<<grid, kThreads, 0, s>>>(g);
+}
+
+int launch_kv_tile_stats(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s, bool with_q) {
+  if (with_q)
+    launch_stats_impl<true>(g, kv_dtype, idx_dtype, s);
+  else
+    launch_stats_impl<false>(g, kv_dtype, idx_dtype, s);
   AKL_LAUNCH_CHECK("kv_tile_stats");
   return AKL_OK;
 }
 
-int launch_kv_means(const Geom& g, cudaStream_t s) {
-  kv_means_kernel<<<g.Hkv, kThreads, 0, s>>>(g);
+int launch_kv_means(const Geom& g, cudaStream_t s, bool fuse_scales) {
+  if (fuse_scales)
+    kv_means_kernel<true><<<g.Hkv, kMeansThreads, 0, s>>>(g);
+  else
+    kv_means_kernel<false><<<g.Hkv, kMeansThreads, 0, s>>>(g);
   AKL_LAUNCH_CHECK("kv_means");
   return AKL_OK;
 }
@@ -365,9 +443,7 @@ int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t
 }
 
 int launch_quantize_q(const Geom& g, cudaStream_t s) {
-  const long long items = static_cast<long long>(g.Hq) * g.mtiles * kQTile;
-  const unsigned blocks = static_cast<unsigned>((items + 7) / 8);
-  quantize_q_kernel<<<blocks, kThreads, 0, s>>>(g);
+  quantize_q_kernel<<<q_ctas(g), kThreads, 0, s>>>(g);
   AKL_LAUNCH_CHECK("quantize_q");
   return AKL_OK;
 }
