@@ -2,7 +2,7 @@
 
 Takes the place of the reference's wheel-or-JIT loader of a pybind11 torch extension
 (src/attn_kernel_lab/kernel.py:151-196).  There is no tensor-library header in the native
-code, so the build is four plain `nvcc -c` runs plus a link, and the binding is `ctypes`
+code, so the build is a handful of plain `nvcc -c` runs plus a link, and the binding is `ctypes`
 over the structs of include/akl.h.
 
 There is no fallback: `load()` raises if the library is missing or lacks a symbol.
@@ -26,7 +26,7 @@ LIB_PATH = PKG_DIR / LIB_NAME
 
 #: Explicit -gencode, never a bare -arch: tcgen05 needs the arch-specific target.
 GENCODE = "arch=compute_100a,code=sm_100a"
-SOURCES = ("akl_prep.cu", "akl_attn_sm100.cu", "akl_merge.cu", "akl_api.cu")
+SOURCES = ("akl_prep.cu", "akl_attn_sm100.cu", "akl_merge.cu", "akl_api.cu", "akl_static_scratch.cu")
 #: Per-file extra flags.  The preprocessing kernels decide quantised bytes, so no
 #: multiply-add may be contracted there.
 EXTRA_FLAGS = {"akl_prep.cu": ("-fmad=false",)}
@@ -35,7 +35,7 @@ EXPORTS = (
     "akl_abi_version", "akl_strerror", "akl_last_cuda_error", "akl_workspace_layout",
     "akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales",
     "akl_kv_transform", "akl_quantize_q", "akl_attention", "akl_attention_dump",
-    "akl_merge_states",
+    "akl_merge_states", "akl_prefill_extend_static_scratch",
 )
 
 AKL_OK = 0
@@ -168,7 +168,7 @@ def load():
         lib.akl_strerror.argtypes = [ctypes.c_int]
         lib.akl_last_cuda_error.restype = ctypes.c_char_p
         lib.akl_workspace_layout.argtypes = [ctypes.POINTER(Plan), ctypes.POINTER(WsLayout)]
-        for name in ("akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales",
+        for name in ("akl_prefill_extend", "akl_prefill_extend_static_scratch", "akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales",
                      "akl_kv_transform", "akl_quantize_q", "akl_attention"):
             fn = getattr(lib, name)
             fn.argtypes = [ctypes.POINTER(Call), ctypes.c_void_p]

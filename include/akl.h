@@ -166,6 +166,18 @@ int akl_attention_dump(const akl_call_t* call, float* s_dump, uint8_t* p_dump, v
 
 int akl_merge_states(const akl_merge_t* m, void* stream);
 
+/* The whole operator (same work and same results as akl_prefill_extend) for callers that cannot
+ * allocate device memory -- an engine plugin that is handed no allocator, or a host whose memory
+ * pool is frozen after start-up.  The workspace is a 16 MiB array built into the library (held by
+ * every GPU that loads it, until the process exits), so `workspace`, `workspace_bytes` and `plan`
+ * of the call are ignored.  Accepted while the workspace layout for the request's own sizes fits
+ * 16 MiB (e.g. N = 4096, T = 512 at 32:4 heads needs 13.1 MiB); beyond that AKL_ERR_CAPACITY.
+ * The first call on a device looks up the array's address: make it before any stream capture.
+ * All calls share the array and it keeps the last call's contents (the status words are cleared
+ * on every call); calls whose GPU work overlaps race.  Calls no cudaMalloc/cudaFree.
+ * This entry point has no counterpart in the reference. */
+int akl_prefill_extend_static_scratch(const akl_call_t* call, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
