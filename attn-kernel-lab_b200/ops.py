@@ -301,21 +301,68 @@ def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, 
     return (out, lse) if request.return_lse else out
 
 
+_side_streams: dict = {}
+
+
+def _streams_for(device, count: int):
+    """`count` side streams per device, created once (stream creation is not capturable)."""
+    import torch
+
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    have = _side_streams.setdefault(key, [])
+    while len(have) < count:
+        have.append(torch.cuda.Stream(device=device))
+    return have[:count]
+
+
 def prefill_extend_batch(requests, *, workspace, sm_scale=None, rotate: bool = True,
                          center_k: bool = True, return_lse: bool = False,
                          capability: OperatorCapability = V1_CAPABILITY):
-    """Run a list of requests back to back on one workspace and the current stream.
+    """Run a list of independent requests; results are exactly those of `prefill_extend` per
+    request (the reference loops per request the same way,
+    engines/sglang/integration/fp8_prefill/backend.py:267-289).
 
     `requests`: iterable of dicts with keys q, k_pool, v_pool, idx, prefix and optionally out,
-    lse_out.  Every request is validated before the first launch; results are exactly those of
-    `prefill_extend` per request (the reference loops the same way per request,
-    engines/sglang/integration/fp8_prefill/backend.py:267-289).  Returns the list of results."""
+    lse_out.  Every request is validated before the first launch.
+
+    `workspace`: one workspace -> the requests run back to back on the current stream.
+    A list/tuple of K workspaces -> request i runs on side stream i % K with workspace i % K:
+    requests are independent units, so the gather/quantise kernels of one request fill the SMs
+    that the last wave of another request's attention kernel leaves idle.  The side streams fork
+    from the current stream and join it again before this function returns (event fork/join, so the
+    whole batch can be captured in one CUDA graph); callers see ordinary stream semantics.
+    Returns the list of results in request order."""
     requests = list(requests)
-    for r in requests:
-        check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"], workspace=workspace,
-                      out=r.get("out"), lse_out=r.get("lse_out"), sm_scale=sm_scale,
-                      return_lse=return_lse, capability=capability)
-    return [prefill_extend(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"],
-                           workspace=workspace, out=r.get("out"), lse_out=r.get("lse_out"),
-                           sm_scale=sm_scale, rotate=rotate, center_k=center_k,
-                           return_lse=return_lse, capability=capability) for r in requests]
+    pool = list(workspace) if isinstance(workspace, (list, tuple)) else [workspace]
+    for i, r in enumerate(requests):
+        check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"],
+                      workspace=pool[i % len(pool)], out=r.get("out"), lse_out=r.get("lse_out"),
+                      sm_scale=sm_scale, return_lse=return_lse, capability=capability)
+
+    def run(r, ws):
+        return prefill_extend(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"], workspace=ws,
+                              out=r.get("out"), lse_out=r.get("lse_out"), sm_scale=sm_scale,
+                              rotate=rotate, center_k=center_k, return_lse=return_lse,
+                              capability=capability)
+
+    if len(pool) == 1 or not requests:
+        return [run(r, pool[0]) for r in requests]
+
+    import torch
+
+    device = requests[0]["q"].device
+    main = torch.cuda.current_stream(device)
+    sides = _streams_for(device, len(pool))
+    fork = torch.cuda.Event()
+    fork.record(main)
+    results = []
+    for k, side in enumerate(sides):
+        side.wait_event(fork)
+    for i, r in enumerate(requests):
+        with torch.cuda.stream(sides[i % len(pool)]):
+            results.append(run(r, pool[i % len(pool)]))
+    for side in sides:
+        join = torch.cuda.Event()
+        join.record(side)
+        main.wait_event(join)
+    return results

@@ -385,6 +385,35 @@ def test_cuda_graph_capture_replay_changed_values_and_poisoned_scratch(pkg, cuda
     assert torch.equal(out, fresh[0]) and ws.status() == 0
 
 
+def test_batch_over_streams_equals_one_by_one_and_can_be_captured(pkg, cuda):
+    """Independent requests spread over two streams/workspaces give byte-identical results, and
+    the fork/join is capturable in one CUDA graph."""
+    shapes = [(37, 65, 28), (200, 1100, 900), (64, 320, 256), (130, 700, 500), (5, 5, 0)]
+    reqs, single = [], []
+    for i, (t, n, p) in enumerate(shapes):
+        case = cases._case(f"b{i}", t, n, p, 24, 4, "scattered", "outlier", 5200 + i)
+        inp = cases.make_inputs(case)
+        q, kp, vp, idx = H.to_dev(inp, cuda)
+        reqs.append({"q": q, "k_pool": kp, "v_pool": vp, "idx": idx, "prefix": p,
+                     "out": torch.empty_like(q), "lse_out": torch.empty((t, 24), dtype=torch.float32, device=cuda)})
+        single.append(pkg.prefill_extend(q, kp, vp, idx, p, return_lse=True))
+    wss = [pkg.plan_workspace(cuda, max_kv_len=1200, max_q_len=256, q_heads=24, kv_heads=4) for _ in range(2)]
+    res = pkg.prefill_extend_batch(reqs, workspace=wss, return_lse=True)
+    torch.cuda.synchronize()
+    for (o, l), (so, sl), r in zip(res, single, reqs):
+        assert o is r["out"] and torch.equal(o, so) and torch.equal(l, sl)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pkg.prefill_extend_batch(reqs, workspace=wss, return_lse=True)
+    for r in reqs:
+        r["out"].fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    for r, (so, sl) in zip(reqs, single):
+        assert torch.equal(r["out"], so) and torch.equal(r["lse_out"], sl)
+    assert all(w.status() == 0 for w in wss)
+
+
 # ------------------------------------------------------------------ full-size properties (config 2 shapes)
 def test_main_profile_shape_sampled_oracle_and_properties(pkg, cuda):
     """One request of the main 24:4 profile at its deepest (prefix 8192, 2048 new tokens):
