@@ -374,6 +374,9 @@ def main():
     args = ap.parse_args()
     LAYERS, REQUESTS = args.layers, args.requests
     if args.impl == "reference":
+        # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU leg is meant to use every core
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(os.cpu_count() or 1)
         reference_arm(args)
         return
 
