@@ -325,9 +325,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
             tmem_ld32(lane_base + kColO + ch * 32 + 32, ob);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              oa[i] = __float_as_uint(__uint_as_float(oa[i]) * alpha);
-              ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
+            for (int i = 0; i < 32; i += 2) {
+              float x0 = __uint_as_float(oa[i]), x1 = __uint_as_float(oa[i + 1]);
+              float y0 = __uint_as_float(ob[i]), y1 = __uint_as_float(ob[i + 1]);
+              mul2(x0, x1, alpha);
+              mul2(y0, y1, alpha);
+              oa[i] = __float_as_uint(x0); oa[i + 1] = __float_as_uint(x1);
+              ob[i] = __float_as_uint(y0); ob[i + 1] = __float_as_uint(y1);
             }
             tmem_st32(lane_base + kColO + ch * 32, oa);
             tmem_st32(lane_base + kColO + ch * 32 + 32, ob);
@@ -405,9 +409,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       for (int i = 0; i < 8; ++i) rmax[i] = -INFINITY;
       if (rem >= kTile - 1) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          s[i] = __uint_as_float(sr[i]) * sc;
+        for (int i = 0; i < 64; i += 2) {
+          s[i] = __uint_as_float(sr[i]);
+          s[i + 1] = __uint_as_float(sr[i + 1]);
+          mul2(s[i], s[i + 1], sc);
           rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
+          rmax[(i + 1) & 7] = fmaxf(rmax[(i + 1) & 7], s[i + 1]);
         }
       } else {
 #pragma unroll
@@ -435,9 +442,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       m_own = m_new;
       float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        s[i] = ex2(fmaf(s[i], kLog2e, pc));
-        part[i & 3] += s[i];
+      for (int i = 0; i < 64; i += 4) {
+        fma2(s[i], s[i + 1], kLog2e, pc);
+        fma2(s[i + 2], s[i + 3], kLog2e, pc);
+        s[i] = ex2(s[i]);
+        s[i + 1] = ex2(s[i + 1]);
+        s[i + 2] = ex2(s[i + 2]);
+        s[i + 3] = ex2(s[i + 3]);
+        add2(part[0], part[1], s[i], s[i + 1]);
+        add2(part[2], part[3], s[i + 2], s[i + 3]);
       }
       l_own = l_own * alpha_l + ((part[0] + part[1]) + (part[2] + part[3])) * t_inv;
 

@@ -143,6 +143,24 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Packed fp32 pairs: one issue slot for two IEEE round-to-nearest operations, bit-identical to
+// the scalar forms.
+__device__ __forceinline__ void mul2(float& a, float& b, float s) {          // a *= s; b *= s
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %2};\n\t"
+      "mul.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b) : "f"(s));
+}
+__device__ __forceinline__ void fma2(float& a, float& b, float m, float c) {  // a = a*m + c; b = b*m + c
+  asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %2};\n\tmov.b64 z, {%3, %3};\n\t"
+      "fma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b) : "f"(m), "f"(c));
+}
+__device__ __forceinline__ void add2(float& a, float& b, float x, float y) {  // a += x; b += y
+  asm("{\n\t.reg .b64 p, q;\n\tmov.b64 p, {%0, %1};\n\tmov.b64 q, {%2, %3};\n\t"
+      "add.rn.f32x2 p, p, q;\n\tmov.b64 {%0, %1}, p;\n\t}"
+      : "+f"(a), "+f"(b) : "f"(x), "f"(y));
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
