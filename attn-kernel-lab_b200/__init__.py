@@ -5,6 +5,7 @@ the declared capability surface, the typed error that separates "outside the sur
 a defect, and the operator entry points.  The directory name is not a Python identifier, so
 import it through `__graft_entry__.package()` (or `importlib`) as `attn_kernel_lab_b200`.
 """
+from .backend import BackendSettings, make_backend_class
 from .capability import (
     CapabilityError,
     GENERALIZATION_CAPABILITY,
@@ -20,7 +21,7 @@ __all__ = [
     "CapabilityError", "GENERALIZATION_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
     "check_supported", "NativeError", "build", "load", "source_build_id", "PrefillRequest",
     "check_request", "plan_workspace", "prefill_extend", "prefill_extend_batch", "CapacityPlan",
-    "FP8PrefillWorkspace", "WorkspaceCapacityError",
+    "FP8PrefillWorkspace", "WorkspaceCapacityError", "BackendSettings", "make_backend_class",
 ]
 
 __version__ = "0.1.0"
