@@ -15,13 +15,14 @@ from .capability import (
 )
 from .kernel import NativeError, build, load, source_build_id
 from .ops import PrefillRequest, check_request, plan_workspace, prefill_extend, prefill_extend_batch
+from .paged import fp8_paged_prefill
 from .quant import CapacityPlan, FP8PrefillWorkspace, WorkspaceCapacityError
 
 __all__ = [
     "CapabilityError", "GENERALIZATION_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
     "check_supported", "NativeError", "build", "load", "source_build_id", "PrefillRequest",
     "check_request", "plan_workspace", "prefill_extend", "prefill_extend_batch", "CapacityPlan",
-    "FP8PrefillWorkspace", "WorkspaceCapacityError", "BackendSettings", "make_backend_class",
+    "FP8PrefillWorkspace", "WorkspaceCapacityError", "BackendSettings", "make_backend_class", "fp8_paged_prefill",
 ]
 
 __version__ = "0.1.0"
