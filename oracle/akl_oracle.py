@@ -47,6 +47,7 @@ BLK = 64          # quantisation tile along the kv axis (quant.py:80)
 MPAD = 128        # query-row padding granule (quant.py:86)
 SLAB = 32768      # normative statistics slab (quant.py:87)
 FP8_MAX = 448.0
+INT8_MAX = 127.0
 F32 = np.float32
 
 
@@ -204,9 +205,10 @@ def _rotate(x, rotation):
 
 @dataclass
 class QPack:
-    q8: np.ndarray        # [H, Mpad, D] uint8 (E4M3 bytes)
+    q8: np.ndarray        # [H, Mpad, D] uint8 (E4M3 bytes, or two's-complement INT8 when qk_i8)
     qscale: np.ndarray    # [H, Mpad] float32, sm_scale folded in
     mpad: int
+    qk_i8: bool = False
 
 
 @dataclass
@@ -221,14 +223,32 @@ class KVPack:
     vinvr: np.ndarray     # [KVH, nt] float32
     vmean: np.ndarray     # [KVH, D] float32
     n: int
+    qk_i8: bool = False   # K bytes are two's-complement INT8 at scale amax/127 (V stays E4M3)
 
 
-def preprocess_q(q: np.ndarray, sm_scale: float, rotation="butterfly") -> QPack:
-    """q [T, H, D] float32 (bf16-valued) -> QPack (quant.py:455-480, FP8 branch).
+def qk_quantise(x: np.ndarray, scale: np.ndarray, qk_i8: bool) -> np.ndarray:
+    """Q/K bytes of one scale group (quant.py:416-430, 471-478): E4M3 of the IEEE quotient, or
+    for INT8 the quotient rounded half-to-even and stored as two's complement, without a clamp
+    (|x| <= amax bounds the quotient at 127 (1 + 2 eps))."""
+    quo = (x / scale).astype(np.float32)
+    if qk_i8:
+        return np.rint(quo).astype(np.int8).view(np.uint8)
+    return e4m3_encode(quo)
+
+
+def qk_decode(b: np.ndarray, qk_i8: bool) -> np.ndarray:
+    """float64 values of Q/K bytes."""
+    if qk_i8:
+        return np.asarray(b, np.uint8).view(np.int8).astype(np.float64)
+    return e4m3_decode_table().astype(np.float64)[np.asarray(b, np.uint8)]
+
+
+def preprocess_q(q: np.ndarray, sm_scale: float, rotation="butterfly", qk_i8: bool = False) -> QPack:
+    """q [T, H, D] float32 (bf16-valued) -> QPack (quant.py:455-480).
 
     Rotate; zero-pad rows to a multiple of 128; per-row amax clamped at 1e-8;
-    scale = amax / 448 (IEEE division); bytes = e4m3(x / scale); exported scale
-    = scale * sm_scale."""
+    scale = amax / lim (IEEE division; lim 448 for E4M3, 127 for INT8); bytes =
+    quantise(x / scale); exported scale = scale * sm_scale."""
     T, H, D = q.shape
     mpad = ceil_to(T, MPAD)
     qf = np.transpose(np.asarray(q, dtype=np.float32), (1, 0, 2))
@@ -237,9 +257,9 @@ def preprocess_q(q: np.ndarray, sm_scale: float, rotation="butterfly") -> QPack:
         qf = np.concatenate([qf, np.zeros((H, mpad - T, D), np.float32)], axis=1)
     amax = np.maximum(qf.max(axis=2), -qf.min(axis=2)).astype(np.float32)
     amax = np.maximum(amax, F32(1e-8))
-    scale = (amax / F32(FP8_MAX)).astype(np.float32)
-    q8 = e4m3_encode((qf / scale[:, :, None]).astype(np.float32))
-    return QPack(q8=q8, qscale=(scale * F32(sm_scale)).astype(np.float32), mpad=mpad)
+    scale = (amax / F32(INT8_MAX if qk_i8 else FP8_MAX)).astype(np.float32)
+    q8 = qk_quantise(qf, scale[:, :, None], qk_i8)
+    return QPack(q8=q8, qscale=(scale * F32(sm_scale)).astype(np.float32), mpad=mpad, qk_i8=qk_i8)
 
 
 def channel_sums_tiled(x: np.ndarray, slab: int = SLAB) -> np.ndarray:
@@ -282,6 +302,7 @@ def preprocess_kv(
     kmean: np.ndarray | None = None,
     vmean: np.ndarray | None = None,
     vsmax_raw: np.ndarray | None = None,
+    qk_i8: bool = False,
 ) -> KVPack:
     """Statistics, K transform, V transform and fold arrays (quant.py:483-695).
 
@@ -329,8 +350,8 @@ def preprocess_kv(
         kf = np.concatenate([kf, np.zeros((KVH, npad - N, D), np.float32)], axis=1)
     kb = kf.reshape(KVH, nt, BLK * D)
     kam = np.maximum(np.maximum(kb.max(axis=2), -kb.min(axis=2)), F32(1e-8)).astype(np.float32)
-    kscale = (kam / F32(FP8_MAX)).astype(np.float32)
-    k8 = e4m3_encode((kf.reshape(KVH, nt, BLK, D) / kscale[:, :, None, None]).astype(np.float32))
+    kscale = (kam / F32(INT8_MAX if qk_i8 else FP8_MAX)).astype(np.float32)
+    k8 = qk_quantise(kf.reshape(KVH, nt, BLK, D), kscale[:, :, None, None], qk_i8)
     k8 = k8.reshape(KVH, npad, D)
 
     # ---- V (quant.py:613-635): centre, pad with zeros, per-tile scale, quantise
@@ -347,7 +368,7 @@ def preprocess_kv(
     vinvr = (F32(1.0) / r).astype(np.float32)
     vscale = (vsmax / F32(FP8_MAX)).astype(np.float32)
     pack = KVPack(k8=k8, kscale=kscale, kmean=kmean, v8=v8, vst=vst, vscale=vscale,
-                  vlog2r=vlog2r, vinvr=vinvr, vmean=vmean, n=N)
+                  vlog2r=vlog2r, vinvr=vinvr, vmean=vmean, n=N, qk_i8=qk_i8)
     pack.vsmax_local = vsmax_local
     return pack
 
@@ -394,7 +415,7 @@ def attention(
     vis_end = np.minimum(prefix + rows + 1, kv_hi)            # exclusive visible end per row
     for hi_, h in enumerate(heads):
         kvh = h // group
-        qf = dec[qp.q8[h, :T]]                                # [T, D]
+        qf = qk_decode(qp.q8[h, :T], qp.qk_i8)                # [T, D]
         qs = qp.qscale[h, :T].astype(np.float64)
         m = np.full(T, -np.inf)
         l = np.zeros(T)
@@ -403,7 +424,7 @@ def attention(
         for t in range(kv_lo // BLK, last + 1):
             lo = t * BLK
             width = min(lo + BLK, n) - lo
-            kf = dec[kv.k8[kvh, lo:lo + width]]               # [w, D]
+            kf = qk_decode(kv.k8[kvh, lo:lo + width], kv.qk_i8)   # [w, D]
             s = (qf @ kf.T) * qs[:, None] * float(kv.kscale[kvh, t])
             cols = lo + np.arange(width)
             visible = cols[None, :] < vis_end[:, None]
@@ -453,13 +474,14 @@ def merge_splits(outs, lses):
 
 
 def reference(q, k, v, prefix, sm_scale=None, return_lse=False, rotation="butterfly",
-              center_k=True, heads=None):
-    """Whole pipeline from bf16-valued float32 inputs (oracle_a.py:289-301, FP8-QK form)."""
+              center_k=True, heads=None, qk_i8=False):
+    """Whole pipeline from bf16-valued float32 inputs (oracle_a.py:289-301; `qk_i8` selects the
+    reference's INT8-QK default, otherwise the FP8-QK form)."""
     T, H, D = q.shape
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
-    qp = preprocess_q(q, sm_scale, rotation=rotation)
-    kv = preprocess_kv(k, v, rotation=rotation, center_k=center_k)
+    qp = preprocess_q(q, sm_scale, rotation=rotation, qk_i8=qk_i8)
+    kv = preprocess_kv(k, v, rotation=rotation, center_k=center_k, qk_i8=qk_i8)
     return attention(qp, kv, prefix, T, group=H // k.shape[1], return_lse=return_lse, heads=heads)
 
 

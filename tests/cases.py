@@ -81,6 +81,9 @@ GOLDEN_CASES = [
     _case("nocen_64_130", 64, 130, 66, 16, 4, "scattered", "outlier", 4106, center_k=False),
 ]
 
+#: cases that also have a fixture for the reference's INT8-QK mode (<name>__i8.npz)
+I8_GOLDEN = ("c1_cpu_oracle", "ragged_37_65", "tiles_128_448", "norot_64_128", "nocen_64_130")
+
 
 def make_inputs(case: dict) -> dict:
     """q [T,H,D] bf16, k_pool/v_pool [pool,KVH,D] bf16|fp16, idx [N] int64 (CPU tensors)."""

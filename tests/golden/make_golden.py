@@ -12,9 +12,13 @@ reference's tests/kernel/test_ops_gpu.py:48-68 -- and stores what came out:
     <case>.npz   inputs' sha256, quantised artifacts (bytes or sha256), scales, means,
                  fold arrays, and the BF16 output + base-2 LSE for a subset of heads.
 
+For the cases named in cases.I8_GOLDEN the same is done once more with qk_i8=True (the
+reference's default INT8-QK mode) into <case>__i8.npz, together with the output of the
+reference's own INT8 oracle oracle_a.reference on the same inputs.
+
 It also extracts, as plain data, the k8 / vt8 / q8 sha256 digests of the FP8-QK,
-fp8-PV single-shot cases of the reference's tests/kernel/golden_bitexact.json into
-bitexact_digests.json (digests only; the case recipe is restated in tests/cases.py).
+fp8-PV single-shot cases of the reference's tests/kernel/golden_bitexact.json (and, under
+"cases_i8", of its INT8-QK cases) into bitexact_digests.json (digests only; the case recipe is restated in tests/cases.py).
 
 The fixtures travel with the repository; the reference checkout does not.
 """
@@ -44,7 +48,7 @@ def sha(t) -> str:
     return hashlib.sha256(np.ascontiguousarray(t).tobytes()).hexdigest()
 
 
-def run_reference(ref_src: pathlib.Path, case: dict) -> dict:
+def run_reference(ref_src: pathlib.Path, case: dict, qk_i8: bool = False) -> dict:
     sys.path.insert(0, str(ref_src))
     from attn_kernel_lab import oracle_a, quant  # the reference, unmodified
 
@@ -57,9 +61,9 @@ def run_reference(ref_src: pathlib.Path, case: dict) -> dict:
     ws = quant.FP8PrefillWorkspace(torch.device("cpu"))
     kvd = quant.gather_quantize_kv(
         ws, k_pool, v_pool, idx.long(), need_vt8=True, need_vb16=False,
-        center_k=case["center_k"], qk_i8=False, rotate=case["rotate"],
+        center_k=case["center_k"], qk_i8=qk_i8, rotate=case["rotate"],
     )
-    q8, qscale, mpad = quant.quantize_q(ws, q, sm_scale, qk_i8=False, rotate=case["rotate"])
+    q8, qscale, mpad = quant.quantize_q(ws, q, sm_scale, qk_i8=qk_i8, rotate=case["rotate"])
     npad = kvd["ntmax"] * quant.BLK
     nt = kvd["ntmax"]
     ksum = ws.get("ksum", (KVH, D), torch.float32).clone()
@@ -73,9 +77,10 @@ def run_reference(ref_src: pathlib.Path, case: dict) -> dict:
     vt8 = kvd["vt8"].view(KVH, nt, D, quant.BLK)
     v8_logical = vt8.permute(0, 1, 3, 2).index_select(2, inv).reshape(KVH, npad, D).contiguous()
 
-    qp = oracle_a.QPack(q8=q8.view(torch.float8_e4m3fn), qscale=qscale, mpad=mpad)
+    qk_view = torch.int8 if qk_i8 else torch.float8_e4m3fn
+    qp = oracle_a.QPack(q8=q8.view(qk_view), qscale=qscale, mpad=mpad)
     kvp = oracle_a.KVPack(
-        k8=kvd["k8"].view(torch.float8_e4m3fn), kscale=kvd["kscale"], kmean=kmean,
+        k8=kvd["k8"].view(qk_view), kscale=kvd["kscale"], kmean=kmean,
         vt8=vt8.view(torch.float8_e4m3fn), vst_scaled=vst, vscale=kvd["vscale"],
         vlog2r=kvd["vlog2r"], vinvr=kvd["vinvr"], vmean=kvd["vmean"], n=N,
     )
@@ -94,6 +99,13 @@ def run_reference(ref_src: pathlib.Path, case: dict) -> dict:
         "out_bf16_bits": out[:, heads].contiguous().view(torch.int16).numpy().view(np.uint16).copy(),
         "lse": lse[:, heads].numpy().copy(),
     }
+    if qk_i8 and case["rotate"] and case["center_k"]:
+        # the reference's own INT8 oracle, whole pipeline, on the gathered rows
+        rows = idx.long()
+        own, own_lse = oracle_a.reference(q, k_pool[rows], v_pool[rows], case["prefix"], sm_scale=sm_scale,
+                                          return_lse=True)
+        rec["oracle_a_out_bf16_bits"] = own[:, heads].contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+        rec["oracle_a_lse"] = own_lse[:, heads].numpy().copy()
     if case.get("store_bytes", False):
         rec["q8"] = q8.numpy().copy()
         rec["k8"] = kvd["k8"].numpy().copy()
@@ -103,18 +115,18 @@ def run_reference(ref_src: pathlib.Path, case: dict) -> dict:
 
 def extract_bitexact(ref_root: pathlib.Path) -> dict:
     j = json.loads((ref_root / "tests" / "kernel" / "golden_bitexact.json").read_text())
-    keep = {}
+    keep, keep_i8 = {}, {}
     for cid, c in j["cases"].items():
         m = c["meta"]
-        if m["qk_i8"] or m["pv"] != "fp8" or m["chunks"] is not None:
+        if m["pv"] != "fp8" or m["chunks"] is not None:
             continue
-        keep[cid] = {
+        (keep_i8 if m["qk_i8"] else keep)[cid] = {
             "meta": {k: m[k] for k in ("shape", "T", "N", "prefix", "H", "KVH", "pool",
                                        "seed", "rotate", "center_k")},
             "artifacts": {k: c["artifacts"][k] for k in ("q8", "k8", "vt8")},
         }
     return {"source": "tests/kernel/golden_bitexact.json (reference), FP8-QK fp8-PV single-shot cases",
-            "env": j["env"], "cases": keep}
+            "env": j["env"], "cases": keep, "cases_i8": keep_i8}
 
 
 def main() -> None:
@@ -128,6 +140,11 @@ def main() -> None:
         path = HERE / f"{case['name']}.npz"
         np.savez_compressed(path, **rec)
         print(f"{case['name']}: wrote {path.name} ({path.stat().st_size / 1024:.0f} KiB)")
+        if case["name"] in case_mod.I8_GOLDEN:
+            rec = run_reference(ref_root / "src", case, qk_i8=True)
+            path = HERE / f"{case['name']}__i8.npz"
+            np.savez_compressed(path, **rec)
+            print(f"{case['name']} (INT8 QK): wrote {path.name} ({path.stat().st_size / 1024:.0f} KiB)")
     (HERE / "bitexact_digests.json").write_text(json.dumps(extract_bitexact(ref_root), indent=1))
     print("wrote bitexact_digests.json")
 

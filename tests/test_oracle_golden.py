@@ -128,6 +128,44 @@ def test_oracle_reproduces_the_reference_byte_for_byte(case):
     assert np.allclose(lse, g["lse"], rtol=0, atol=2e-6)
 
 
+_I8_CASES = [c for c in cases.GOLDEN_CASES if c["name"] in cases.I8_GOLDEN]
+
+
+@pytest.mark.parametrize("case", _I8_CASES, ids=lambda c: c["name"])
+def test_int8_qk_oracle_reproduces_the_reference_byte_for_byte(case):
+    """The reference's default mode: Q and K as INT8 at amax/127, rounded half-to-even, no clamp
+    (quant.py:416-430, 471-478); everything after the bytes as in the FP8 test above."""
+    g = np.load(GOLDEN / f"{case['name']}__i8.npz")
+    inp = cases.make_inputs(case)
+    assert tsha(inp["q"]) == str(g["in_sha_q"]) and tsha(inp["k_pool"]) == str(g["in_sha_k_pool"])
+    rows = inp["idx"]
+    q = inp["q"].float().numpy()
+    k = inp["k_pool"][rows].float().numpy()
+    v = inp["v_pool"][rows].float().numpy()
+    rot = "sequential" if case["rotate"] else None
+    qp = O.preprocess_q(q, case["sm_scale"], rotation=rot, qk_i8=True)
+    kv = O.preprocess_kv(k, v, rotation=rot, center_k=case["center_k"], kmean=g["kmean"], vmean=g["vmean"],
+                         qk_i8=True)
+    assert sha(qp.q8) == str(g["sha_q8"]) and sha(kv.k8) == str(g["sha_k8"]) and sha(kv.v8) == str(g["sha_v8"])
+    for name, mine in (("qscale", qp.qscale), ("kscale", kv.kscale), ("vst", kv.vst), ("vscale", kv.vscale)):
+        assert np.array_equal(bits(mine), bits(g[name])), name
+    assert np.abs(qp.q8.view(np.int8).astype(np.int32)).max() <= 127
+    heads = g["heads"].tolist()
+    kv.vlog2r = g["vlog2r"].copy()
+    out, lse = O.attention(qp, kv, case["prefix"], case["T"], case["H"] // case["KVH"],
+                           return_lse=True, heads=heads)
+    assert np.array_equal(O.f32_to_bf16_bits(out), g["out_bf16_bits"])
+    assert np.allclose(lse, g["lse"], rtol=0, atol=2e-6)
+    if "oracle_a_out_bf16_bits" in g.files:
+        # the reference's own INT8 oracle (oracle_a.reference, unmodified) on the same inputs: a
+        # different reduction order for the means, so agreement is to rounding, not to the bit
+        theirs = O.bf16_bits_to_f32(g["oracle_a_out_bf16_bits"])
+        rel = np.linalg.norm((out - theirs).reshape(-1, 256), axis=1) / \
+            np.maximum(np.linalg.norm(theirs.reshape(-1, 256), axis=1), 1e-30)
+        assert np.median(rel) < 2e-3 and rel.max() < 5e-2
+        assert np.abs(lse - g["oracle_a_lse"]).max() < 5e-3
+
+
 @pytest.mark.parametrize("case", cases.GOLDEN_CASES, ids=lambda c: c["name"])
 def test_cuda_order_twin_against_the_unmodified_reference(case):
     """The order the CUDA kernels use (butterfly rotation, tiled channel sums) against the
@@ -180,6 +218,29 @@ def test_reference_golden_digests(cid):
     assert sha(vt8) == arts["vt8"]
     assert (sha(kv.k8) == arts["k8"]) == (cid not in _K8_GPU_ONLY)
     assert (sha(qp.q8[:, :meta["T"]]) == arts["q8"]) == (cid not in _Q8_GPU_ONLY)
+
+
+#: INT8-QK cases of the same matrix: every digest reproduces except one rotated, centred k8 that
+#: depends on the GPU GEMM's summation order.
+_DIGESTS_I8 = json.loads((GOLDEN / "bitexact_digests.json").read_text())["cases_i8"]
+_K8_I8_GPU_ONLY = {"ragged|qki8|rot1|cen1|pvfp8"}
+
+
+@pytest.mark.parametrize("cid", sorted(_DIGESTS_I8), ids=lambda s: s.replace("|", "-"))
+def test_reference_golden_digests_int8_qk(cid):
+    meta, arts = _DIGESTS_I8[cid]["meta"], _DIGESTS_I8[cid]["artifacts"]
+    inp = cases.bitexact_inputs(meta)
+    rows = inp["idx"]
+    k = inp["k_pool"][rows].float().numpy()
+    v = inp["v_pool"][rows].float().numpy()
+    rot = "sequential" if meta["rotate"] else None
+    qp = O.preprocess_q(inp["q"].float().numpy(), 1.0 / 16.0, rotation=rot, qk_i8=True)
+    kv = O.preprocess_kv(k, v, rotation=rot, center_k=meta["center_k"], qk_i8=True)
+    kvh, npad, d = kv.v8.shape
+    vt8 = kv.v8.reshape(kvh, npad // 64, 64, d)[:, :, SIGMA64, :].transpose(0, 1, 3, 2)
+    assert sha(vt8) == arts["vt8"]
+    assert (sha(kv.k8) == arts["k8"]) == (cid not in _K8_I8_GPU_ONLY)
+    assert sha(qp.q8[:, :meta["T"]]) == arts["q8"]
 
 
 # ------------------------------------------------------------------ operator properties the reference tests
