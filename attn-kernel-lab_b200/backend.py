@@ -18,10 +18,9 @@ What is kept from the reference, by name and meaning:
     `_K_CENTER`, `_HADAMARD`, `_QK`, `_BF16_HEADS`, `_DEBUG` (:93-113).
 
 What differs:
-  * `_QK`: only the FP8-QK operand type is built for sm_100a.  Unset means "fp8" here; an explicit
-    "int8" (the reference default) makes every forward take the inherited path, with the reason
-    logged once.  `_BF16_HEADS` non-empty does the same (the bf16-PV lane is not on the declared
-    surface).
+  * `_BF16_HEADS` non-empty makes every forward take the inherited path, with the reason logged
+    once (the bf16-PV lane is not on the declared surface and is not built); `_QK` accepts "int8"
+    (default, as in the reference) and "fp8", anything else is treated the same way.
   * requests whose head counts are outside the declared capability surface (for example a
     tensor-parallel shard with 6:1 heads) take the inherited path instead of raising;
   * the per-request Python loop of three calls (:267-289) is one `prefill_extend_batch` call that
@@ -55,7 +54,7 @@ class BackendSettings:
     min_extend: int = 0
     center_k: bool = True
     rotate: bool = True
-    qk: str = "fp8"
+    qk: str = "int8"
     bf16_heads: str = ""
     debug: bool = False
     streams: int = 1
@@ -69,7 +68,7 @@ class BackendSettings:
             min_extend=int(env.get("SGLANG_FP8_PREFILL_MIN_EXTEND", "0")),
             center_k=env.get("SGLANG_FP8_PREFILL_K_CENTER", "1") != "0",
             rotate=env.get("SGLANG_FP8_PREFILL_HADAMARD", "1") != "0",
-            qk=env.get("SGLANG_FP8_PREFILL_QK", "fp8").strip().lower(),
+            qk=env.get("SGLANG_FP8_PREFILL_QK", "int8").strip().lower(),
             bf16_heads=env.get("SGLANG_FP8_PREFILL_BF16_HEADS", "").strip(),
             debug=env.get("SGLANG_FP8_PREFILL_DEBUG") == "1",
             streams=max(1, int(env.get("SGLANG_FP8_PREFILL_STREAMS", "1"))),
@@ -77,8 +76,8 @@ class BackendSettings:
 
     def unbuilt_mode(self) -> Optional[str]:
         """Why the configured operator variant cannot run here, or None."""
-        if self.qk != "fp8":
-            return f"SGLANG_FP8_PREFILL_QK={self.qk!r}: only the fp8 QK operand type is built for sm_100a"
+        if self.qk not in ("int8", "fp8"):
+            return f"SGLANG_FP8_PREFILL_QK={self.qk!r}: the QK operand type is int8 or fp8"
         if self.bf16_heads:
             return "SGLANG_FP8_PREFILL_BF16_HEADS is set: the bf16-PV lane is not built"
         return None
@@ -124,9 +123,9 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
             elif self._unbuilt:
                 logger.warning("[fp8_prefill] every forward takes the inherited path: %s", self._unbuilt)
             else:
-                logger.info("[fp8_prefill] enabled: min_tokens=%d min_extend=%d page_size=%d streams=%d",
-                            self._settings.min_tokens, self._settings.min_extend, self._page_size,
-                            self._settings.streams)
+                logger.info("[fp8_prefill] enabled: qk=%s min_tokens=%d min_extend=%d page_size=%d streams=%d",
+                            self._settings.qk, self._settings.min_tokens, self._settings.min_extend,
+                            self._page_size, self._settings.streams)
 
         # ---- metadata time -------------------------------------------------------------
         def init_forward_metadata(self, forward_batch):
@@ -246,7 +245,8 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
                 self._workspaces.append(FP8PrefillWorkspace(q.device))
             workspace = self._workspaces[0] if want == 1 else self._workspaces[:want]
             ops.prefill_extend_batch(requests, workspace=workspace, sm_scale=layer.scaling,
-                                     rotate=self._settings.rotate, center_k=self._settings.center_k)
+                                     qk_i8=self._settings.qk == "int8", rotate=self._settings.rotate,
+                                     center_k=self._settings.center_k)
             return out.view(-1, heads * HEAD_DIM)
 
     _Backend.__name__ = _Backend.__qualname__ = name

@@ -82,6 +82,7 @@ constexpr uint32_t kSmemBytes = kOffAlpha + 2048 + 1024;   // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256;
 constexpr uint32_t kIdescQK = idesc_e4m3(128, 128);
+constexpr uint32_t kIdescQKi8 = idesc_s8(128, 128);
 constexpr uint32_t kIdescPV = idesc_e4m3(128, 256);
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLog2_448 = 8.807354922057604f;
@@ -168,12 +169,15 @@ __device__ __forceinline__ uint64_t desc_at(uint32_t lo, uint32_t byte_off) {
 }
 __device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
 
-// QK^T of one 128-key pair: 8 MMAs of K = 32 (two 128-byte planes x four 32-byte steps).
+// QK^T of one 128-key pair: 8 MMAs of K = 32 (two 128-byte planes x four 32-byte steps);
+// E4M3 operands with an fp32 accumulator, or INT8 operands with an exact s32 accumulator.
+template <bool kI8>
 __device__ __forceinline__ void issue_qk(uint32_t q_lo, uint32_t k_lo, uint32_t tmem_s) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t off = (k >> 2) * kPlaneBytes + (k & 3) * 32;
-    mma_f8_ss(tmem_s, desc_at(q_lo, off), desc_at(k_lo, off), kIdescQK, k > 0 ? 1u : 0u);
+    if (kI8) mma_i8_ss(tmem_s, desc_at(q_lo, off), desc_at(k_lo, off), kIdescQKi8, k > 0 ? 1u : 0u);
+    else mma_f8_ss(tmem_s, desc_at(q_lo, off), desc_at(k_lo, off), kIdescQK, k > 0 ? 1u : 0u);
   }
 }
 
@@ -183,7 +187,14 @@ __device__ __forceinline__ void issue_pv(uint32_t p_lo, uint32_t v_lo, uint32_t 
   mma_f8_ss(tmem_o, desc_at(p_lo, 32), desc_at(v_lo, 32), kIdescPV, 1u);
 }
 
-template <bool kDump>
+// One QK^T accumulator word as a float: the fp32 sum itself, or the s32 sum converted (exact:
+// |sum| <= 256 * 127 * 127 < 2^24).
+template <bool kI8>
+__device__ __forceinline__ float acc_value(uint32_t word) {
+  return kI8 ? __int2float_rn(static_cast<int>(word)) : __uint_as_float(word);
+}
+
+template <bool kDump, bool kI8>
 __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_slot;
@@ -277,7 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
         if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + b, (n - 1) & 1);   // both groups have read S(u-2)
         if (!ok) break;
         tc_fence_after();
-        issue_qk(q_lo, desc_lo(smem + kOffK + b * 32768), tmem + kColS + b * 128);
+        issue_qk<kI8>(q_lo, desc_lo(smem + kOffK + b * 32768), tmem + kColS + b * 128);
         tc_commit(ctx.bars + (B_SFULL + b) * 8);
         tc_commit(ctx.bars + (B_KEMPTY + b) * 8);
       }
@@ -399,7 +410,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       if (kDump) {
         float* dst = g.dbg_s + ((((static_cast<size_t>(h) * g.mtiles + qt) * g.nt + j) * kQTile + row) * kTile);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) dst[i] = __uint_as_float(sr[i]);
+        for (int i = 0; i < 64; ++i) dst[i] = acc_value<kI8>(sr[i]);
       }
       const float sc = qs * t_ks;
       const int rem = limit - j * kTile;
@@ -410,8 +421,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       if (rem >= kTile - 1) {
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
-          s[i] = __uint_as_float(sr[i]);
-          s[i + 1] = __uint_as_float(sr[i + 1]);
+          s[i] = acc_value<kI8>(sr[i]);
+          s[i + 1] = acc_value<kI8>(sr[i + 1]);
           mul2(s[i], s[i + 1], sc);
           rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
           rmax[(i + 1) & 7] = fmaxf(rmax[(i + 1) & 7], s[i + 1]);
@@ -419,7 +430,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
       } else {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          const float v = __uint_as_float(sr[i]) * sc;
+          const float v = acc_value<kI8>(sr[i]) * sc;
           s[i] = (i <= rem) ? v : -INFINITY;
           rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
         }
@@ -541,23 +552,28 @@ int launch_attention(const Geom& g, cudaStream_t s, bool dump) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { note_cuda_error(e, "cudaGetDevice"); return AKL_ERR_CUDA; }
   if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    // idempotent, so a race between host threads only repeats the call
-    e = cudaFuncSetAttribute(attn_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(attn)"); return AKL_ERR_CUDA; }
+    // idempotent, so a race between host threads only repeats the calls
+    const void* kernels[4] = {
+        reinterpret_cast<const void*>(attn_sm100_kernel<false, false>), reinterpret_cast<const void*>(attn_sm100_kernel<false, true>),
+        reinterpret_cast<const void*>(attn_sm100_kernel<true, false>), reinterpret_cast<const void*>(attn_sm100_kernel<true, true>)};
+    for (const void* k : kernels) {
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(attn)"); return AKL_ERR_CUDA; }
+    }
     if (dev < 64) configured[dev].store(true, std::memory_order_release);
   }
   dim3 grid(g.mtiles, g.Hq);
+  const bool i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
 #ifdef AKL_TRACE
-  if (dump)   // development build: the dump pointer receives the timeline, not the scores
-    attn_sm100_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(g);
-#else
-  if (dump)
-    attn_sm100_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(g);
+  dump = false;   // development build: the dump pointer receives the timeline, not the scores
 #endif
-  else
-    attn_sm100_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(g);
+  if (dump) {
+    if (i8) attn_sm100_kernel<true, true><<<grid, kThreads, kSmemBytes, s>>>(g);
+    else attn_sm100_kernel<true, false><<<grid, kThreads, kSmemBytes, s>>>(g);
+  } else {
+    if (i8) attn_sm100_kernel<false, true><<<grid, kThreads, kSmemBytes, s>>>(g);
+    else attn_sm100_kernel<false, false><<<grid, kThreads, kSmemBytes, s>>>(g);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) { note_cuda_error(e, "attn_sm100_kernel"); return AKL_ERR_CUDA; }
   return AKL_OK;

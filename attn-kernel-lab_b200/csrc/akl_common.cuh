@@ -18,6 +18,7 @@ constexpr int kQTile = AKL_Q_TILE;        // 128 query rows per CTA
 constexpr int kPlaneBytes = 128 * 128;    // one [128 rows][128 B] swizzled plane
 constexpr int kImageBytes = 2 * kPlaneBytes;  // one 128-row x 256-byte operand tile
 constexpr float kFp8Max = 448.0f;
+constexpr float kInt8Max = 127.0f;
 constexpr int kSlabTiles = AKL_STAT_SLAB / AKL_KV_TILE;
 
 // Everything a phase kernel needs, resolved on the host from akl_call_t + layout.
@@ -96,6 +97,18 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
 
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
   return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+// float -> INT8 byte, round half to even (the quotient is bounded by 127 (1 + 2 eps), so there
+// is nothing to clamp).  Four bytes, first value in bits 0-7.
+__device__ __forceinline__ uint32_t cvt_s8x4(float a, float b, float c, float d) {
+  return (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) | ((static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << 8) |
+         ((static_cast<uint32_t>(__float2int_rn(c)) & 0xFFu) << 16) | (static_cast<uint32_t>(__float2int_rn(d)) << 24);
+}
+
+// Q/K bytes in the call's QK operand type
+__device__ __forceinline__ uint32_t cvt_qk_x4(bool i8, float a, float b, float c, float d) {
+  return i8 ? cvt_s8x4(a, b, c, d) : cvt_e4m3x4(a, b, c, d);
 }
 
 // 256-point fast Walsh-Hadamard transform over a warp: lane l holds elements

@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
   }
   const bool center = is_v || (g.flags & AKL_FLAG_CENTER_K);
   const bool rotate = !is_v && (g.flags & AKL_FLAG_ROTATE);
+  const bool qk_i8 = !is_v && (g.flags & AKL_FLAG_QK_I8);     // V is E4M3 in both modes
 
   float x[8][8];
   float amax = 0.f;
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) a = fmaxf(a, sm_red[i]);
     a = fmaxf(a, 1e-8f);
-    scale = __fdiv_rn(a, kFp8Max);
+    scale = __fdiv_rn(a, qk_i8 ? kInt8Max : kFp8Max);
     if (threadIdx.x == 0) g.kscale[kvh * g.ntiles_cap + t] = scale;
   } else {
     scale = g.vst[kvh * g.ntiles_cap + t];
@@ -278,8 +279,8 @@ __global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
     float y[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[i][c], scale);
-    lo[i] = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
-    hi[i] = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+    lo[i] = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
+    hi[i] = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
   }
 
   const int pair = t >> 1, half = t & 1;
@@ -360,12 +361,13 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
       for (int c = 0; c < 8; ++c) x[k][c] = 0.f;
     }
     amax = fmaxf(warp_max(amax), 1e-8f);
-    const float scale = __fdiv_rn(amax, kFp8Max);
+    const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
+    const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
     float y[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[k][c], scale);
-    const uint32_t lo = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
-    const uint32_t hi = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+    const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
+    const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
     const int tile = rr[k] >> 7, r7 = rr[k] & 127, plane = lane >> 4;
     uint8_t* img = g.q8 + (static_cast<size_t>(hh[k]) * g.mtiles_cap + tile) * kImageBytes;
     *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(r7, (lane & 15) * 8)) = make_uint2(lo, hi);

@@ -43,7 +43,7 @@ AKL_ERR_INVALID, AKL_ERR_UNSUPPORTED, AKL_ERR_CAPACITY = -1, -2, -3
 AKL_ERR_CUDA, AKL_ERR_ALIGN, AKL_ERR_TIMEOUT = -4, -5, -6
 AKL_KV_BF16, AKL_KV_FP16 = 0, 1
 AKL_IDX_I64, AKL_IDX_I32 = 0, 1
-AKL_FLAG_ROTATE, AKL_FLAG_CENTER_K = 1, 2
+AKL_FLAG_ROTATE, AKL_FLAG_CENTER_K, AKL_FLAG_QK_I8 = 1, 2, 4
 
 
 class Plan(ctypes.Structure):

@@ -8,8 +8,9 @@ native call (`akl_prefill_extend`, include/akl.h) that gathers, quantises, atten
 permute-copy (ops.py:597-609 of the reference).
 
 Differences a caller can see, all deliberate:
-  * `qk_i8` defaults to False and True is refused with a CapabilityError: this build computes
-    QK in FP8 E4M3 on tcgen05; the reference's INT8-QK mode is not built.
+  * `qk_i8` defaults to False (FP8 E4M3 QK, the mode this build is measured in); `qk_i8=True`
+    selects the reference's default INT8-QK mode (ops.py:496), an exact s32 QK^T on the same
+    tensor-core path.
   * `idx` may be int32 as well as int64 (the reference requires int64, ops.py:248-253).
   * `prefill_extend_batch` runs a list of requests back to back on one workspace.
 
@@ -249,12 +250,6 @@ def plan_workspace(device, *, max_kv_len: int, max_q_len: int, q_heads: int | No
                                need_lse=return_lse)
 
 
-def _refuse_variants(qk_i8: bool) -> None:
-    if qk_i8:
-        _reject("qk_i8=True (INT8 QK) is not built for sm_100a: this operator computes QK in FP8 "
-                "E4M3; pass qk_i8=False", field="qk_i8", value=True, supported=(False,))
-
-
 def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, lse_out=None,
                    sm_scale=None, qk_i8: bool = False, rotate: bool = True, center_k: bool = True,
                    return_lse: bool = False, capability: OperatorCapability = V1_CAPABILITY):
@@ -270,7 +265,8 @@ def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, 
     request = check_request(q, k_pool, v_pool, idx, prefix, workspace=workspace, out=out,
                             lse_out=lse_out, sm_scale=sm_scale, return_lse=return_lse,
                             capability=capability)
-    _refuse_variants(qk_i8)
+    if not isinstance(qk_i8, bool):
+        raise TypeError(f"qk_i8 must be a bool, got {type(qk_i8).__name__}")
 
     # ---- everything below touches the device -------------------------------------------
     import torch
@@ -294,7 +290,7 @@ def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, 
         ws, q=q, k_pool=k_pool, v_pool=v_pool, idx=idx, out=out, lse_out=lse,
         q_len=request.q_len, kv_len=request.kv_len, prefix=request.prefix,
         q_heads=request.q_heads, kv_heads=request.kv_heads, sm_scale=request.sm_scale,
-        rotate=rotate, center_k=center_k)
+        rotate=rotate, center_k=center_k, qk_i8=qk_i8)
     with torch.cuda.device(q.device):
         code = lib.akl_prefill_extend(ctypes.byref(call), torch.cuda.current_stream(q.device).cuda_stream)
     kernel_mod.check(code, "akl_prefill_extend")
@@ -315,7 +311,7 @@ def _streams_for(device, count: int):
     return have[:count]
 
 
-def prefill_extend_batch(requests, *, workspace, sm_scale=None, rotate: bool = True,
+def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = False, rotate: bool = True,
                          center_k: bool = True, return_lse: bool = False,
                          capability: OperatorCapability = V1_CAPABILITY):
     """Run a list of independent requests; results are exactly those of `prefill_extend` per
@@ -342,7 +338,7 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, rotate: bool = T
     def run(r, ws):
         return prefill_extend(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"], workspace=ws,
                               out=r.get("out"), lse_out=r.get("lse_out"), sm_scale=sm_scale,
-                              rotate=rotate, center_k=center_k, return_lse=return_lse,
+                              qk_i8=qk_i8, rotate=rotate, center_k=center_k, return_lse=return_lse,
                               capability=capability)
 
     if len(pool) == 1 or not requests:

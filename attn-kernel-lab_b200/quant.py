@@ -257,8 +257,8 @@ def _idx_code(t: torch.Tensor) -> int:
 
 def make_call(ws: FP8PrefillWorkspace, *, q=None, k_pool, v_pool, idx, out=None, lse_out=None,
               q_len: int, kv_len: int, prefix: int, q_heads: int, kv_heads: int, sm_scale: float,
-              rotate: bool = True, center_k: bool = True, kv_pos0: int = 0, n_total: int = 0,
-              tile0_global: int = 0, ntiles_global: int = 0) -> "_kernel.Call":
+              rotate: bool = True, center_k: bool = True, qk_i8: bool = False, kv_pos0: int = 0,
+              n_total: int = 0, tile0_global: int = 0, ntiles_global: int = 0) -> "_kernel.Call":
     """Fill an `akl_call_t` from tensors (pointers only; nothing is copied or launched)."""
     mk, mq, hq, hkv = ws.dims
     c = _kernel.Call()
@@ -275,7 +275,8 @@ def make_call(ws: FP8PrefillWorkspace, *, q=None, k_pool, v_pool, idx, out=None,
     c.q_heads, c.kv_heads = q_heads, kv_heads
     c.kv_dtype = _dtype_code(k_pool)
     c.idx_dtype = _idx_code(idx) if idx.dtype in (torch.int64, torch.int32) else _kernel.AKL_IDX_I64
-    c.flags = (_kernel.AKL_FLAG_ROTATE if rotate else 0) | (_kernel.AKL_FLAG_CENTER_K if center_k else 0)
+    c.flags = ((_kernel.AKL_FLAG_ROTATE if rotate else 0) | (_kernel.AKL_FLAG_CENTER_K if center_k else 0)
+               | (_kernel.AKL_FLAG_QK_I8 if qk_i8 else 0))
     c.sm_scale = float(sm_scale)
     c.kv_pos0, c.n_total = kv_pos0, n_total
     c.tile0_global, c.ntiles_global = tile0_global, ntiles_global
@@ -286,22 +287,14 @@ def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _refuse_i8(qk_i8: bool) -> None:
-    if qk_i8:
-        from .capability import CapabilityError
-        raise CapabilityError(
-            "qk_i8=True (INT8 QK) is not built for sm_100a; this operator computes QK in FP8 "
-            "E4M3 (pass qk_i8=False)", field="qk_i8", value=True, supported=(False,))
-
-
 def gather_quantize_kv(ws: FP8PrefillWorkspace, k_buffer, v_buffer, idx, need_vt8: bool = True,
                        need_vb16: bool = False, center_k: bool = True, qk_i8: bool = False,
                        rotate: bool = True) -> dict:
     """Gather + statistics + transform + quantise the request's K/V (quant.py:483-695).
 
     Returns the same keys as the reference; `k8` / `vt8` are this build's tile images -- use
-    `ws.k8_logical(n)` / `ws.v8_logical(n)` for position-order bytes."""
-    _refuse_i8(qk_i8)
+    `ws.k8_logical(n)` / `ws.v8_logical(n)` for position-order bytes.  `qk_i8` selects INT8 K bytes
+    at amax/127 (the reference's default) instead of E4M3 at amax/448."""
     if need_vb16 or not need_vt8:
         raise ValueError("only the all-FP8-PV lane (need_vt8=True, need_vb16=False) is built")
     n, kvh = int(idx.shape[0]), int(k_buffer.shape[1])
@@ -309,7 +302,7 @@ def gather_quantize_kv(ws: FP8PrefillWorkspace, k_buffer, v_buffer, idx, need_vt
     ws.ensure(n, ws.dims[1] if ws.dims else 1, hq, kvh)
     lib = _kernel.load()
     call = make_call(ws, k_pool=k_buffer, v_pool=v_buffer, idx=idx, q_len=1, kv_len=n, prefix=0,
-                     q_heads=hq, kv_heads=kvh, sm_scale=1.0, rotate=rotate, center_k=center_k)
+                     q_heads=hq, kv_heads=kvh, sm_scale=1.0, rotate=rotate, center_k=center_k, qk_i8=qk_i8)
     st = _stream(k_buffer.device)
     for fn in ("akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales", "akl_kv_transform"):
         _kernel.check(getattr(lib, fn)(ctypes.byref(call), st), fn)
@@ -323,15 +316,14 @@ def gather_quantize_kv(ws: FP8PrefillWorkspace, k_buffer, v_buffer, idx, need_vt
 def quantize_q(ws: FP8PrefillWorkspace, q, sm_scale: float, qk_i8: bool = False,
                rotate: bool = True):
     """-> (q8 tile images, qscale [H, Mpad] f32 per row with sm_scale folded, Mpad)
-    (quant.py:433-480)."""
-    _refuse_i8(qk_i8)
+    (quant.py:433-480).  `qk_i8`: INT8 bytes at amax/127 instead of E4M3 at amax/448."""
     t, h = int(q.shape[0]), int(q.shape[1])
     kvh = ws.dims[3] if ws.dims and ws.dims[2] == h else DECLARED_KV_HEADS
     ws.ensure(ws.dims[0] if ws.dims else 1, t, h, kvh)
     lib = _kernel.load()
     # the pools are not read by this phase; any 16-byte-aligned device address satisfies the check
     call = make_call(ws, q=q, k_pool=q, v_pool=q, idx=q, q_len=t, kv_len=1, prefix=0, q_heads=h,
-                     kv_heads=kvh, sm_scale=sm_scale, rotate=rotate)
+                     kv_heads=kvh, sm_scale=sm_scale, rotate=rotate, qk_i8=qk_i8)
     _kernel.check(lib.akl_quantize_q(ctypes.byref(call), _stream(q.device)), "akl_quantize_q")
     mpad = _ceil_to(t, MPAD)
     return ws.view("q8"), ws.view("qscale")[:, :mpad], mpad

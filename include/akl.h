@@ -49,6 +49,8 @@ enum { AKL_IDX_I64 = 0, AKL_IDX_I32 = 1 };
 /* akl_call_t.flags */
 #define AKL_FLAG_ROTATE 1u    /* Hadamard-rotate Q and K (reference kwarg rotate, ops.py:497) */
 #define AKL_FLAG_CENTER_K 2u  /* subtract the K channel mean (reference kwarg center_k, ops.py:498) */
+#define AKL_FLAG_QK_I8 4u     /* Q and K as INT8 at amax/127 with an exact s32 QK^T (reference kwarg qk_i8,
+                               * its default, ops.py:496; quant.py:416-430, 471-478); clear = FP8 E4M3 QK */
 
 /* Capacity plan: the maxima a workspace is laid out for.
  * Replaces quant.FP8PrefillWorkspace.reserve / CapacityPlan (quant.py:175-196, :253-336). */

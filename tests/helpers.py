@@ -46,23 +46,23 @@ def gathered(inp: dict):
             inp["v_pool"][rows].float().numpy())
 
 
-def workspace_packs(ws, T: int, N: int):
+def workspace_packs(ws, T: int, N: int, qk_i8: bool = False):
     """The kernel's own quantised artifacts as oracle packs (position-order bytes)."""
     nt = (N + 63) // 64
     mpad = (T + 127) // 128 * 128
     qp = O.QPack(q8=ws.q8_logical(T).cpu().numpy(),
-                 qscale=ws.view("qscale")[:, :mpad].cpu().numpy(), mpad=mpad)
+                 qscale=ws.view("qscale")[:, :mpad].cpu().numpy(), mpad=mpad, qk_i8=qk_i8)
     kv = O.KVPack(
         k8=ws.k8_logical(N).cpu().numpy(), kscale=ws.view("kscale")[:, :nt].cpu().numpy(),
         kmean=ws.view("kmean").cpu().numpy(), v8=ws.v8_logical(N).cpu().numpy(),
         vst=ws.view("vst")[:, :nt].cpu().numpy(), vscale=ws.view("vscale").cpu().numpy(),
         vlog2r=ws.view("vlog2r")[:, :nt].cpu().numpy(), vinvr=ws.view("vinvr")[:, :nt].cpu().numpy(),
-        vmean=ws.view("vmean").cpu().numpy(), n=N)
+        vmean=ws.view("vmean").cpu().numpy(), n=N, qk_i8=qk_i8)
     return qp, kv
 
 
 def run_phases(pkg, ws, q, kp, vp, idx, prefix, sm_scale, *, out=None, lse=None, rotate=True,
-               center_k=True, dump=False):
+               center_k=True, dump=False, qk_i8=False):
     """Drive the phase entry points of the C ABI one by one (same work as akl_prefill_extend)."""
     from attn_kernel_lab_b200 import kernel as K, quant
 
@@ -74,7 +74,7 @@ def run_phases(pkg, ws, q, kp, vp, idx, prefix, sm_scale, *, out=None, lse=None,
     lse = torch.empty((T, H), dtype=torch.float32, device=q.device) if lse is None else lse
     call = quant.make_call(ws, q=q, k_pool=kp, v_pool=vp, idx=idx, out=out, lse_out=lse, q_len=T,
                            kv_len=N, prefix=prefix, q_heads=H, kv_heads=KVH, sm_scale=sm_scale,
-                           rotate=rotate, center_k=center_k)
+                           rotate=rotate, center_k=center_k, qk_i8=qk_i8)
     st = torch.cuda.current_stream(q.device).cuda_stream
     for fn in ("akl_kv_tile_stats", "akl_quantize_q", "akl_kv_means", "akl_kv_scales",
                "akl_kv_transform"):

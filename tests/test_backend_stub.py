@@ -47,10 +47,10 @@ class Recorder:
     def __init__(self):
         self.calls = []
 
-    def __call__(self, requests, *, workspace, sm_scale=None, rotate=True, center_k=True, **kw):
+    def __call__(self, requests, *, workspace, sm_scale=None, qk_i8=False, rotate=True, center_k=True, **kw):
         requests = list(requests)
         self.calls.append({"requests": requests, "workspace": workspace, "sm_scale": sm_scale,
-                           "rotate": rotate, "center_k": center_k})
+                           "qk_i8": qk_i8, "rotate": rotate, "center_k": center_k})
         for i, r in enumerate(requests):
             r["out"].fill_(float(i + 1))
         return [r["out"] for r in requests]
@@ -80,6 +80,7 @@ def test_qualifying_forward_runs_the_operator_from_the_snapshot(backend_mod, mon
     assert pool.writes == [(1, 812)], "the chunk is written through to the pool, once, before the operator"
     (call,) = rec.calls
     assert call["sm_scale"] == layer.scaling and call["rotate"] and call["center_k"]
+    assert call["qk_i8"] is True, "INT8 QK is the default operand type, as in the reference"
     assert call["workspace"] == ("workspace", "cpu")
     r0, r1 = call["requests"]
     assert r0["prefix"] == 9000 and r1["prefix"] == 8500
@@ -104,7 +105,7 @@ def test_save_kv_cache_false_skips_the_write(backend_mod, monkeypatch):
 
 @pytest.mark.parametrize("why, kwargs", [
     ("disabled", dict(env={"SGLANG_FP8_PREFILL_DISABLE": "1"})),
-    ("int8 QK is not built", dict(env={"SGLANG_FP8_PREFILL_QK": "int8"})),
+    ("unknown QK operand type", dict(env={"SGLANG_FP8_PREFILL_QK": "fp4"})),
     ("bf16-PV lane is not built", dict(env={"SGLANG_FP8_PREFILL_BF16_HEADS": "0,3"})),
     ("short request", dict(prefix=(9000, 100), extend=(512, 300))),
     ("short extend", dict(env={"SGLANG_FP8_PREFILL_MIN_EXTEND": "400"})),
@@ -148,12 +149,13 @@ def test_other_forward_modes_and_missing_metadata_fall_back(backend_mod, monkeyp
 def test_knobs_reach_the_operator_and_streams_get_their_own_workspaces(backend_mod, monkeypatch):
     be, fb, layer, (q, k, v), _, _ = _setup(
         backend_mod, monkeypatch, env={"SGLANG_FP8_PREFILL_K_CENTER": "0", "SGLANG_FP8_PREFILL_HADAMARD": "0",
+                                       "SGLANG_FP8_PREFILL_QK": "fp8",
                                        "SGLANG_FP8_PREFILL_STREAMS": "4", "SGLANG_FP8_PREFILL_MIN_TOKENS": "100"})
     rec = _patch_operator(backend_mod, monkeypatch)
     be.init_forward_metadata(fb)
     be.forward_extend(q, k, v, layer, fb)
     (call,) = rec.calls
-    assert call["rotate"] is False and call["center_k"] is False
+    assert call["rotate"] is False and call["center_k"] is False and call["qk_i8"] is False
     assert isinstance(call["workspace"], list) and len(call["workspace"]) == 2    # min(streams, requests)
 
 

@@ -13,13 +13,14 @@ import sglang_stubs as S
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("streams", ["1", "2"])
-def test_forward_extend_equals_per_request_operator_calls(pkg, cuda, monkeypatch, streams):
+@pytest.mark.parametrize("streams, qk", [("1", "fp8"), ("2", "fp8"), ("2", "int8")])
+def test_forward_extend_equals_per_request_operator_calls(pkg, cuda, monkeypatch, streams, qk):
     from attn_kernel_lab_b200 import backend
 
     monkeypatch.setenv("SGLANG_FP8_PREFILL_MIN_TOKENS", "64")
     monkeypatch.setenv("SGLANG_FP8_PREFILL_STREAMS", streams)
-    for key in ("DISABLE", "QK", "BF16_HEADS", "MIN_EXTEND", "K_CENTER", "HADAMARD"):
+    monkeypatch.setenv("SGLANG_FP8_PREFILL_QK", qk)
+    for key in ("DISABLE", "BF16_HEADS", "MIN_EXTEND", "K_CENTER", "HADAMARD"):
         monkeypatch.delenv("SGLANG_FP8_PREFILL_" + key, raising=False)
     cls = backend.make_backend_class(S.BaseBackend, S.ForwardMode.EXTEND)
     g = torch.Generator().manual_seed(77)
@@ -56,13 +57,14 @@ def test_forward_extend_equals_per_request_operator_calls(pkg, cuda, monkeypatch
     for r, (p, e) in enumerate(zip(prefix, extend)):
         idx = table[r + 1, :p + e].long().to(cuda)
         want, lse = pkg.prefill_extend(q3[row0:row0 + e], pool.k[2], pool.v[2], idx, p,
-                                       sm_scale=layer.scaling, return_lse=True)
+                                       sm_scale=layer.scaling, return_lse=True, qk_i8=qk == "int8")
         torch.cuda.synchronize()
         got = out.view(tokens, Hq, 256)[row0:row0 + e]
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"request {r}"
         if r == 1:      # and the operator itself against the float64 oracle, once
             ref = O.reference(q3[row0:row0 + e].float().cpu().numpy(), pool.k[2][idx].float().cpu().numpy(),
-                              pool.v[2][idx].float().cpu().numpy(), p, sm_scale=layer.scaling)
+                              pool.v[2][idx].float().cpu().numpy(), p, sm_scale=layer.scaling,
+                              qk_i8=qk == "int8")
             rel = H.row_rel(got.float().cpu().numpy(), ref)
             assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.97
         row0 += e

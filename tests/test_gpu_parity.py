@@ -27,6 +27,7 @@ import helpers as H
 pytestmark = pytest.mark.gpu
 GOLDEN = pathlib.Path(__file__).resolve().parent / "golden"
 DIGESTS = json.loads((GOLDEN / "bitexact_digests.json").read_text())["cases"]
+DIGESTS_I8 = json.loads((GOLDEN / "bitexact_digests.json").read_text())["cases_i8"]
 SIGMA32 = [0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15,
            16, 17, 24, 25, 18, 19, 26, 27, 20, 21, 28, 29, 22, 23, 30, 31]
 SIGMA64 = [(j // 32) * 32 + SIGMA32[j % 32] for j in range(64)]
@@ -70,17 +71,21 @@ def assert_prep_exact(ws, qp, kv, T, N):
 
 
 # ------------------------------------------------------------------ preprocessing
+QK_MODES = pytest.mark.parametrize("qk_i8", [False, True], ids=["qk_fp8", "qk_int8"])
+
+
+@QK_MODES
 @pytest.mark.parametrize("case", ALL_CASES, ids=lambda c: c["name"])
-def test_preprocessing_is_bit_exact(pkg, cuda, case):
+def test_preprocessing_is_bit_exact(pkg, cuda, case, qk_i8):
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
     ws = pkg.FP8PrefillWorkspace(cuda)
     H.run_phases(pkg, ws, q, kp, vp, idx, case["prefix"], case["sm_scale"], rotate=case["rotate"],
-                 center_k=case["center_k"])
+                 center_k=case["center_k"], qk_i8=qk_i8)
     qf, kf, vf = H.gathered(inp)
     rot = "butterfly" if case["rotate"] else None
-    qp = O.preprocess_q(qf, case["sm_scale"], rotation=rot)
-    kv = O.preprocess_kv(kf, vf, rotation=rot, center_k=case["center_k"])
+    qp = O.preprocess_q(qf, case["sm_scale"], rotation=rot, qk_i8=qk_i8)
+    kv = O.preprocess_kv(kf, vf, rotation=rot, center_k=case["center_k"], qk_i8=qk_i8)
     assert_prep_exact(ws, qp, kv, case["T"], case["N"])
     assert ws.status() == 0
 
@@ -121,18 +126,39 @@ def test_reference_golden_digests_on_the_gpu(pkg, cuda, cid):
         assert sha(ws.k8_logical(meta["N"]).cpu().numpy()) == arts["k8"]
 
 
+@pytest.mark.parametrize("cid", sorted(DIGESTS_I8), ids=lambda s: s.replace("|", "-"))
+def test_reference_golden_digests_int8_qk_on_the_gpu(pkg, cuda, cid):
+    """The INT8-QK cases of the same matrix: V bytes in every case; K and Q bytes wherever no
+    rotation GEMM is involved (there the arithmetic is the same division and rounding)."""
+    meta, arts = DIGESTS_I8[cid]["meta"], DIGESTS_I8[cid]["artifacts"]
+    inp = cases.bitexact_inputs(meta)
+    q, kp, vp, idx = H.to_dev(inp, cuda)
+    ws = pkg.FP8PrefillWorkspace(cuda)
+    H.run_phases(pkg, ws, q, kp, vp, idx, meta["prefix"], 1.0 / 16.0, rotate=meta["rotate"],
+                 center_k=meta["center_k"], qk_i8=True)
+    v8 = ws.v8_logical(meta["N"]).cpu().numpy()
+    kvh, npad, d = v8.shape
+    vt8 = v8.reshape(kvh, npad // 64, 64, d)[:, :, SIGMA64, :].transpose(0, 1, 3, 2)
+    assert sha(vt8) == arts["vt8"]
+    if not meta["rotate"]:
+        assert sha(ws.k8_logical(meta["N"]).cpu().numpy()) == arts["k8"]
+        assert sha(ws.q8_logical(meta["T"]).cpu().numpy()[:, :meta["T"]]) == arts["q8"]
+
+
 # ------------------------------------------------------------------ attention
+@QK_MODES
 @pytest.mark.parametrize("case", ALL_CASES, ids=lambda c: c["name"])
-def test_attention_scores_probabilities_and_output(pkg, cuda, case):
+def test_attention_scores_probabilities_and_output(pkg, cuda, case, qk_i8):
     T, N, Hq, KVH, prefix = case["T"], case["N"], case["H"], case["KVH"], case["prefix"]
     g = Hq // KVH
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
     ws = pkg.FP8PrefillWorkspace(cuda)
     out, lse, (s_dump, p_dump) = H.run_phases(pkg, ws, q, kp, vp, idx, prefix, case["sm_scale"],
-                                              rotate=case["rotate"], center_k=case["center_k"], dump=True)
+                                              rotate=case["rotate"], center_k=case["center_k"], dump=True,
+                                              qk_i8=qk_i8)
     assert ws.status() == 0
-    qp, kv = H.workspace_packs(ws, T, N)
+    qp, kv = H.workspace_packs(ws, T, N, qk_i8)
     sd, pd = s_dump.cpu().numpy(), p_dump.cpu().numpy()
     got, got_lse = out.float().cpu().numpy(), lse.cpu().numpy()
     dec = O.e4m3_decode_table().astype(np.float64)
@@ -142,14 +168,14 @@ def test_attention_scores_probabilities_and_output(pkg, cuda, case):
     flips_formula = total_p = 0
     for h in range(Hq):
         kvh = h // g
-        S = dec[qp.q8[h]] @ dec[kv.k8[kvh]].T           # exact: every partial sum fits a double
+        S = O.qk_decode(qp.q8[h], qk_i8) @ O.qk_decode(kv.k8[kvh], qk_i8).T   # exact: every partial sum fits a double
         for qt in range(mt):
             hi = min(prefix + qt * 128 + 128, N)
             ntile = (hi + 63) // 64
             for j in range(ntile):                      # raw accumulators
                 ref = S[qt * 128:(qt + 1) * 128, j * 64:(j + 1) * 64]
                 err = np.abs(sd[h, qt, j][:, :ref.shape[1]] - ref).max()
-                assert err <= 2e-6 * max(1.0, np.abs(ref).max()), "QK^T accumulators"
+                assert err <= (0.0 if qk_i8 else 2e-6 * max(1.0, np.abs(ref).max())), "QK^T accumulators"
             l = np.zeros(128, np.float32)
             acc = np.zeros((128, 256))
             m = None
@@ -238,6 +264,27 @@ def test_against_the_reference_output_fixture(pkg, cuda):
     rel = H.row_rel(got, ref)
     assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.97
     assert np.abs(lse.cpu().numpy()[:, heads] - g["lse"]).max() < 5e-3
+
+
+@pytest.mark.parametrize("name", cases.I8_GOLDEN)
+def test_int8_qk_public_entry_against_the_reference_fixtures(pkg, cuda, name):
+    """qk_i8=True (the reference's default mode) through the public entry, against the outputs the
+    unmodified reference produced on the same seeded inputs: its quant.py + oracle_a.attention
+    composition, and its whole-pipeline INT8 oracle oracle_a.reference where the fixture has it."""
+    case = next(c for c in cases.GOLDEN_CASES if c["name"] == name)
+    g = np.load(GOLDEN / f"{name}__i8.npz")
+    _, _, (out, lse) = _public(pkg, cuda, case, return_lse=True, qk_i8=True)
+    _, _, fp8_out = _public(pkg, cuda, case, qk_i8=False)
+    assert not torch.equal(out, fp8_out), "the two QK operand types are different operators"
+    heads = g["heads"].tolist()
+    got = out.float().cpu().numpy()[:, heads]
+    for key_o, key_l in (("out_bf16_bits", "lse"), ("oracle_a_out_bf16_bits", "oracle_a_lse")):
+        if key_o not in g.files:
+            continue
+        ref = O.bf16_bits_to_f32(g[key_o])
+        rel = H.row_rel(got, ref)
+        assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.97, key_o
+        assert np.abs(lse.cpu().numpy()[:, heads] - g[key_l]).max() < 5e-3, key_l
 
 
 def test_capacity_equals_grow_and_reuse_after_a_larger_request(pkg, cuda):

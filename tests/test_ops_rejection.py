@@ -106,10 +106,14 @@ def test_out_must_not_alias_q(pkg):
     assert info.value.field == "out"
 
 
-def test_int8_qk_is_refused_as_a_capability_not_a_defect(pkg):
-    with pytest.raises(pkg.CapabilityError, match=r"qk_i8=True .* is not built") as info:
-        pkg.prefill_extend(**_call(), qk_i8=True)
-    assert info.value.field == "qk_i8" and info.value.supported == (False,)
+def test_int8_qk_is_accepted_and_reaches_the_device_check(pkg):
+    """Both QK operand types pass validation; on CPU tensors the call then stops where every
+    accepted request stops, at the missing device (there is no CPU path)."""
+    for mode in (True, False):
+        with pytest.raises(RuntimeError, match="no CPU path"):
+            pkg.prefill_extend(**_call(), qk_i8=mode)
+    with pytest.raises(TypeError, match="qk_i8"):
+        pkg.prefill_extend(**_call(), qk_i8="int8")
 
 
 def test_bf16_pv_lane_is_refused_at_planning(pkg):
