@@ -107,7 +107,7 @@ def merge_states(parts_o, parts_lse, out=None, lse_out=None):
 
 # ------------------------------------------------------------------ KV-axis split of one request
 def kv_split_local(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_total: int, kv_lo: int,
-                   sm_scale: float, rotate: bool = True, center_k: bool = True,
+                   sm_scale: float, rotate: bool = True, center_k: bool = True, qk_i8: bool = False,
                    all_reduce_sum=None, all_reduce_max=None, phases=None):
     """One rank's share of a KV-split request: statistics made global through the two
     callbacks, then transform + attention over local positions [kv_lo, kv_lo + len(idx_local)).
@@ -137,7 +137,7 @@ def kv_split_local(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_total: in
     call = _quant.make_call(
         ws, q=q, k_pool=k_pool, v_pool=v_pool, idx=idx_local, out=out, lse_out=lse, q_len=T,
         kv_len=max(n_local, 1), prefix=prefix, q_heads=Hq, kv_heads=Hkv, sm_scale=sm_scale,
-        rotate=rotate, center_k=center_k, kv_pos0=kv_lo, n_total=n_total,
+        rotate=rotate, center_k=center_k, qk_i8=qk_i8, kv_pos0=kv_lo, n_total=n_total,
         tile0_global=kv_lo // _quant.BLK, ntiles_global=ntg)
     ktsum, vtsum = ws.view("ktsum"), ws.view("vtsum")
     ktsum[:ntg].zero_()
@@ -164,7 +164,7 @@ def kv_split_local(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_total: in
 
 def prefill_extend_kv_split(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_total: int,
                             kv_lo: int, sm_scale: float, group=None, rotate: bool = True,
-                            center_k: bool = True, phases=None, merge=None):
+                            center_k: bool = True, qk_i8: bool = False, phases=None, merge=None):
     """KV-axis split of one long request across the ranks of `group` (default: world).
 
     Every rank passes the full `q`, its own slice of the page table (`idx_local`, global
@@ -184,7 +184,7 @@ def prefill_extend_kv_split(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_
 
     o_i, lse_i = kv_split_local(ws, q, k_pool, v_pool, idx_local, prefix, n_total=n_total,
                                 kv_lo=kv_lo, sm_scale=sm_scale, rotate=rotate, center_k=center_k,
-                                all_reduce_sum=ar_sum, all_reduce_max=ar_max, phases=phases)
+                                qk_i8=qk_i8, all_reduce_sum=ar_sum, all_reduce_max=ar_max, phases=phases)
     return exchange_and_merge(o_i, lse_i, group=group, merge=merge)
 
 

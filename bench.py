@@ -48,6 +48,7 @@ HQ, HKV, D = 24, 4, 256
 POOL_ROWS = 446_464
 LAYERS = 16
 REQUESTS = 8
+QK_I8 = False          # --qk int8 runs the reference's default INT8-QK mode instead of FP8-QK
 T_EXT = 2048
 SM_SCALE = 1.0 / 16.0
 NOMINAL_FP8_TFLOPS = 4500.0
@@ -180,7 +181,7 @@ def run_step(pkg, wl, ws):
         pkg.prefill_extend_batch(
             [{"q": r["q"][layer], "k_pool": kp, "v_pool": vp, "idx": r["idx"], "prefix": r["prefix"],
               "out": r["out"][layer]} for r in wl["reqs"]],
-            workspace=ws, sm_scale=SM_SCALE)
+            workspace=ws, sm_scale=SM_SCALE, qk_i8=QK_I8)
 
 
 def time_attention_kernel(torch, pkg, wl, ws, reps: int = 5):
@@ -196,7 +197,7 @@ def time_attention_kernel(torch, pkg, wl, ws, reps: int = 5):
     for r in wl["reqs"]:
         call = quant.make_call(ws, q=r["q"][0], k_pool=kp, v_pool=vp, idx=r["idx"], out=r["out"][0],
                                q_len=r["T"], kv_len=r["N"], prefix=r["prefix"], q_heads=HQ, kv_heads=HKV,
-                               sm_scale=SM_SCALE)
+                               sm_scale=SM_SCALE, qk_i8=QK_I8)
         for fn in ("akl_kv_tile_stats", "akl_quantize_q", "akl_kv_means", "akl_kv_scales", "akl_kv_transform"):
             K.check(getattr(lib, fn)(ctypes.byref(call), st), fn)
         K.check(lib.akl_attention(ctypes.byref(call), st), "akl_attention")        # warm
@@ -273,7 +274,7 @@ def time_e2e(torch, pkg, wl, ws, steps: int, warmup: int):
                 kp.index_copy_(0, new_rows, s["k"][:r["T"]])       # the chunk's K/V enter the paged pool
                 vp.index_copy_(0, new_rows, s["v"][:r["T"]])
                 pkg.prefill_extend(s["q"][:r["T"]], kp, vp, r["idx"], r["prefix"], workspace=ws,
-                                   out=s["out"][:r["T"]], sm_scale=SM_SCALE)
+                                   out=s["out"][:r["T"]], sm_scale=SM_SCALE, qk_i8=QK_I8)
                 s["computed"].record(compute)
                 with torch.cuda.stream(d2h):
                     d2h.wait_event(s["computed"])
@@ -321,7 +322,7 @@ def cpu_oracle_sample(repeats: int = 1):
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        oracle.reference(q, k, v, prefix, sm_scale=SM_SCALE)
+        oracle.reference(q, k, v, prefix, sm_scale=SM_SCALE, qk_i8=QK_I8)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
     return best, flops(prefix, t), t
@@ -357,7 +358,7 @@ def reference_arm(args):
 
 # --------------------------------------------------------------------------------------
 def main():
-    global LAYERS, REQUESTS
+    global LAYERS, REQUESTS, QK_I8
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -369,10 +370,12 @@ def main():
                     help="requests per GPU (default 8; fewer only for profiling captures)")
     ap.add_argument("--streams", type=int, default=4,
                     help="workspaces/streams the independent requests of a layer are spread over")
+    ap.add_argument("--qk", default="fp8", choices=["fp8", "int8"],
+                    help="QK operand type: fp8 (the measured configuration) or int8 (the reference's default mode)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
-    LAYERS, REQUESTS = args.layers, args.requests
+    LAYERS, REQUESTS, QK_I8 = args.layers, args.requests, args.qk == "int8"
     if args.impl == "reference":
         # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU leg is meant to use every core
         for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
@@ -466,8 +469,8 @@ def main():
         line = {
             "metric": "inclusive_tflops", "value": value, "unit": "TF/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": per_step * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
-            "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 QK, fp8_e4m3 PV" if QK_I8 else "fp8_e4m3", "data": "synthetic",
             "tokens_per_s": wl["tokens_per_step"] * world / per_step,
             "token_layers_per_s": wl["tokens_per_step"] * LAYERS * world / per_step,
             "frac_of_nominal_dense_fp8": value / (NOMINAL_FP8_TFLOPS * world),
@@ -475,7 +478,8 @@ def main():
                        "requests_per_gpu": REQUESTS, "layers": LAYERS,
                        "extend_tokens": T_EXT, "prefixes": [r["prefix"] for r in wl["reqs"]],
                        "q_heads": HQ, "kv_heads": HKV, "head_dim": D, "pool_slots": POOL_ROWS,
-                       "kv_dtype": "bfloat16", "page_size": 1, "partition": f"requests x{world}", "streams_per_gpu": args.streams,
+                       "qk": args.qk, "kv_dtype": "bfloat16", "page_size": 1, "partition": f"requests x{world}",
+                       "streams_per_gpu": args.streams,
                        "l2": "inputs larger than L2 (29.3 GB of pools, 3.2 GB of queries per step)"},
             "e2e": ({"value": e2e_value, "unit": "TF/s", "h2d_bytes_per_step": h2d_b, "d2h_bytes_per_step": d2h_b}
                     if e2e_value is not None else None),
