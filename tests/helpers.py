@@ -114,3 +114,85 @@ def kernel_softmax_restated(S_raw, qscale_rows, kscale, vlog2r, vinvr, prefix, r
         p = np.where(np.isfinite(sv), p, 0).astype(np.float32)
         yield j, p, alpha, m_new
         m = m_new
+
+
+def oracle_row_block(q, k, v, prefix, sm_scale, head: int, kv_head: int, r0: int, r1: int, *, qk_i8=False,
+                     rotation="butterfly", center_k=True):
+    """The float64 oracle for query rows r0:r1 of one q head, from position-order CPU tensors
+    q [T,H,256], k/v [N,KVH,256]: per-row Q quantisation and per-head K/V statistics are
+    independent of the other rows and heads, so a block is exact, and cheap at any length.
+    Returns (out [R,256] float32 bf16-rounded, lse [R] float32)."""
+    qp, kv = oracle_block_packs(q, k, v, sm_scale, head, kv_head, r0, r1, qk_i8=qk_i8, rotation=rotation,
+                                center_k=center_k)
+    out, lse = O.attention(qp, kv, prefix + r0, r1 - r0, 1, return_lse=True)
+    return out[:, 0], lse[:, 0]
+
+
+def oracle_block_packs(q, k, v, sm_scale, head: int, kv_head: int, r0: int, r1: int, *, qk_i8=False,
+                       rotation="butterfly", center_k=True):
+    """Oracle packs for query rows r0:r1 of one q head and its KV head (see oracle_row_block);
+    attend with prefix + r0 as the prefix and group 1."""
+    qf = q[r0:r1, head:head + 1].float().numpy()
+    kf = k[:, kv_head:kv_head + 1].float().numpy()
+    vf = v[:, kv_head:kv_head + 1].float().numpy()
+    qp = O.preprocess_q(qf, sm_scale, rotation=rotation, qk_i8=qk_i8)
+    kv = O.preprocess_kv(kf, vf, rotation=rotation, center_k=center_k, qk_i8=qk_i8)
+    return qp, kv
+
+
+def assert_block_close(got_out, got_lse, ref_out, ref_lse, what=""):
+    """Tolerance-level agreement of a row block with the oracle (quantised bytes equal up to rare
+    one-code flips, so rows agree to rounding; a flipped P byte may move a peaked row more)."""
+    rel = row_rel(got_out, ref_out)
+    assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.95, (what, float(np.median(rel)), float(rel.max()))
+    fin = np.isfinite(ref_lse)
+    assert np.array_equal(np.isfinite(got_lse), fin), what
+    assert np.abs(got_lse[fin] - ref_lse[fin]).max() < 5e-3, what
+
+
+def emulated_kv_split(pkg, q, kp, vp, idx, prefix, sm_scale, world, *, qk_i8=False):
+    """The multi-GPU KV-axis split run as consecutive per-rank phase calls on ONE device (ranks
+    that would wait on one another never share a GPU): tile sums per rank, the disjoint-support
+    SUM, means per rank, the MAX of the raw V amax, then transform, Q and attention per rank, and
+    the merge kernel.  Returns (merged_out, merged_lse, workspaces, ranges, outs, lses)."""
+    from attn_kernel_lab_b200 import dist as D, kernel as K, quant
+
+    lib = K.load()
+    dev = q.device
+    st = torch.cuda.current_stream(dev).cuda_stream
+    T, Hq = int(q.shape[0]), int(q.shape[1])
+    Hkv = int(kp.shape[1])
+    n_total = int(idx.numel())
+    ranges = D.kv_split_ranges(n_total, world)
+    ntg = (n_total + 63) // 64
+    wss = [pkg.FP8PrefillWorkspace(dev) for _ in ranges]
+    calls, outs, lses = [], [], []
+    slices = [idx[lo:hi].contiguous() for lo, hi in ranges]      # kept alive for the launches
+    for ws, (lo, hi), part in zip(wss, ranges, slices):
+        ws.ensure(n_total, T, Hq, Hkv)
+        o = torch.empty_like(q)
+        l = torch.empty((T, Hq), dtype=torch.float32, device=dev)
+        c = quant.make_call(ws, q=q, k_pool=kp, v_pool=vp, idx=part, out=o, lse_out=l, q_len=T,
+                            kv_len=hi - lo, prefix=prefix, q_heads=Hq, kv_heads=Hkv, sm_scale=sm_scale,
+                            qk_i8=qk_i8, kv_pos0=lo, n_total=n_total, tile0_global=lo // 64,
+                            ntiles_global=ntg)
+        ws.view("ktsum")[:ntg].zero_()
+        ws.view("vtsum")[:ntg].zero_()
+        K.check(lib.akl_kv_tile_stats(ctypes.byref(c), st), "stats")
+        calls.append(c), outs.append(o), lses.append(l)
+    ksum = sum(ws.view("ktsum")[:ntg] for ws in wss)
+    vsum = sum(ws.view("vtsum")[:ntg] for ws in wss)
+    for ws, c in zip(wss, calls):
+        ws.view("ktsum")[:ntg].copy_(ksum)
+        ws.view("vtsum")[:ntg].copy_(vsum)
+        K.check(lib.akl_kv_means(ctypes.byref(c), st), "means")
+    vsmax = torch.stack([ws.view("vsmax") for ws in wss]).amax(dim=0)
+    for ws, c in zip(wss, calls):
+        ws.view("vsmax").copy_(vsmax)
+        for fn in ("akl_kv_scales", "akl_kv_transform", "akl_quantize_q", "akl_attention"):
+            K.check(getattr(lib, fn)(ctypes.byref(c), st), fn)
+    merged, mlse = D.merge_states(outs, lses)
+    torch.cuda.synchronize()
+    assert all(ws.status() == 0 for ws in wss)
+    del slices
+    return merged, mlse, wss, ranges, outs, lses

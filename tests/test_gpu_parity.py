@@ -537,44 +537,8 @@ def test_kv_axis_split_emulated_on_one_gpu(pkg, cuda):
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
     n_total, T, prefix = case["N"], case["T"], case["prefix"]
-    ranges = D.kv_split_ranges(n_total, 4)
+    merged, mlse, wss, ranges, outs, lses = H.emulated_kv_split(pkg, q, kp, vp, idx, prefix, case["sm_scale"], 4)
     assert ranges[-1][1] == n_total and ranges[2][1] - ranges[2][0] > 0
-    wss = [pkg.FP8PrefillWorkspace(cuda) for _ in ranges]
-    for ws in wss:
-        ws.ensure(n_total, T, 32, 4)
-    ntg = (n_total + 63) // 64
-    # phase A on every "rank": tile sums into its own array, then the disjoint-support SUM
-    from attn_kernel_lab_b200 import kernel as K, quant
-
-    lib = K.load()
-    st = torch.cuda.current_stream().cuda_stream
-    calls, outs, lses = [], [], []
-    slices = [idx[lo:hi].contiguous() for lo, hi in ranges]      # kept alive for the launches
-    for ws, (lo, hi), part in zip(wss, ranges, slices):
-        o = torch.empty_like(q)
-        l = torch.empty((T, 32), dtype=torch.float32, device=cuda)
-        c = quant.make_call(ws, q=q, k_pool=kp, v_pool=vp, idx=part, out=o, lse_out=l,
-                            q_len=T, kv_len=hi - lo, prefix=prefix, q_heads=32, kv_heads=4,
-                            sm_scale=case["sm_scale"], kv_pos0=lo, n_total=n_total,
-                            tile0_global=lo // 64, ntiles_global=ntg)
-        ws.view("ktsum")[:ntg].zero_()
-        ws.view("vtsum")[:ntg].zero_()
-        K.check(lib.akl_kv_tile_stats(ctypes.byref(c), st), "stats")
-        calls.append(c), outs.append(o), lses.append(l)
-    ksum = sum(ws.view("ktsum")[:ntg] for ws in wss)
-    vsum = sum(ws.view("vtsum")[:ntg] for ws in wss)
-    for ws, c in zip(wss, calls):
-        ws.view("ktsum")[:ntg].copy_(ksum)
-        ws.view("vtsum")[:ntg].copy_(vsum)
-        K.check(lib.akl_kv_means(ctypes.byref(c), st), "means")
-    vsmax = torch.stack([ws.view("vsmax") for ws in wss]).amax(dim=0)
-    for ws, c in zip(wss, calls):
-        ws.view("vsmax").copy_(vsmax)
-        for fn in ("akl_kv_scales", "akl_kv_transform", "akl_quantize_q", "akl_attention"):
-            K.check(getattr(lib, fn)(ctypes.byref(c), st), fn)
-    merged, mlse = D.merge_states(outs, lses)
-    torch.cuda.synchronize()
-    assert all(ws.status() == 0 for ws in wss)
 
     qf, kf, vf = H.gathered(inp)
     whole = O.preprocess_kv(kf, vf)
