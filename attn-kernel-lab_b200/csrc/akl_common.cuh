@@ -129,10 +129,13 @@ __device__ __forceinline__ void fwht256(float (&x)[8], int lane) {
   }
 #pragma unroll
   for (int m = 1; m < 32; m <<= 1) {
+    // upper partner: o - x, lower partner: x + o; as one fused op, fma(+-1, x, o) rounds the
+    // same exact sum once, so the bits are those of the add / subtract
+    const float sign = (lane & m) ? -1.f : 1.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float o = __shfl_xor_sync(0xffffffffu, x[i], m);
-      x[i] = (lane & m) ? __fsub_rn(o, x[i]) : __fadd_rn(x[i], o);
+      x[i] = __fmaf_rn(sign, x[i], o);
     }
   }
 #pragma unroll

@@ -27,7 +27,7 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta);
 // Flat grid: CTAs [0, nt*Hkv) take one (tile, kv head) each; with kWithQ the CTAs after them
 // quantise Q rows, so that the two independent passes share one launch and overlap.
 template <int KV_DTYPE, int IDX_DTYPE, bool kWithQ>
-__global__ void __launch_bounds__(kThreads) kv_tile_stats_kernel(Geom g) {
+__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_kernel(Geom g) {
   __shared__ float sm_k[8][kD];
   __shared__ float sm_v[8][kD];
   __shared__ float sm_mx[8][kD];
@@ -44,31 +44,38 @@ __global__ void __launch_bounds__(kThreads) kv_tile_stats_kernel(Geom g) {
   // pool rows of this warp's 8 positions
   long long pr = 0;
   if (lane < 8 && row0 + lane < g.N) pr = load_idx<IDX_DTYPE>(g.idx, row0 + lane);
-  uint4 kraw[8], vraw[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    long long p = __shfl_sync(0xffffffffu, pr, i);
-    if (row0 + i < g.N) {
-      size_t off = (static_cast<size_t>(p) * g.Hkv + kvh) * kD + lane * 8;
-      kraw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.k_pool) + off));
-      vraw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.v_pool) + off));
-    }
-  }
+  // the warp's 8 rows in four passes of 2 (4 x 16 bytes in flight per thread, four CTAs per SM);
+  // the running sums see the rows in position order either way
   float ks[8], vs[8], mx[8], mn[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) { ks[c] = 0.f; vs[c] = 0.f; mx[c] = -INFINITY; mn[c] = INFINITY; }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (row0 + i < g.N) {
-      float kx[8], vx[8];
-      unpack8<KV_DTYPE>(kraw[i], kx);
-      unpack8<KV_DTYPE>(vraw[i], vx);
+  for (int pass = 0; pass < 4; ++pass) {
+    uint4 kraw[2], vraw[2];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        ks[c] = __fadd_rn(ks[c], kx[c]);
-        vs[c] = __fadd_rn(vs[c], vx[c]);
-        mx[c] = fmaxf(mx[c], vx[c]);
-        mn[c] = fminf(mn[c], vx[c]);
+    for (int ii = 0; ii < 2; ++ii) {
+      const int i = pass * 2 + ii;
+      long long p = __shfl_sync(0xffffffffu, pr, i);
+      if (row0 + i < g.N) {
+        size_t off = (static_cast<size_t>(p) * g.Hkv + kvh) * kD + lane * 8;
+        kraw[ii] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.k_pool) + off));
+        vraw[ii] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(g.v_pool) + off));
+      }
+    }
+#pragma unroll
+    for (int ii = 0; ii < 2; ++ii) {
+      const int i = pass * 2 + ii;
+      if (row0 + i < g.N) {
+        float kx[8], vx[8];
+        unpack8<KV_DTYPE>(kraw[ii], kx);
+        unpack8<KV_DTYPE>(vraw[ii], vx);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          ks[c] = __fadd_rn(ks[c], kx[c]);
+          vs[c] = __fadd_rn(vs[c], vx[c]);
+          mx[c] = fmaxf(mx[c], vx[c]);
+          mn[c] = fminf(mn[c], vx[c]);
+        }
       }
     }
   }
@@ -206,7 +213,7 @@ __global__ void __launch_bounds__(kThreads) kv_scales_kernel(Geom g) {
 //    (quant.py:589-668).  blockIdx.z: 0 = K, 1 = V.
 // ---------------------------------------------------------------------------
 template <int KV_DTYPE, int IDX_DTYPE>
-__global__ void __launch_bounds__(kThreads) kv_transform_kernel(Geom g) {
+__global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
   constexpr int kVRow = 80;                       // padded 64-byte row, keeps 16 B alignment
   __shared__ float sm_red[8];
   __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
