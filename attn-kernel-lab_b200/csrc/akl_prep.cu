@@ -304,14 +304,11 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
     // transpose through shared memory: sm_vt[d][key]
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      uint32_t b0 = 0, b1 = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t src0 = (c < 4) ? lo[i] : hi[i];
-        const uint32_t src1 = (c < 4) ? lo[i + 4] : hi[i + 4];
-        b0 |= ((src0 >> (8 * (c & 3))) & 0xFFu) << (8 * i);
-        b1 |= ((src1 >> (8 * (c & 3))) & 0xFFu) << (8 * i);
-      }
+      // byte (c & 3) of rows 0-3 and of rows 4-7: three byte permutes per word
+      const uint32_t* src = (c < 4) ? lo : hi;
+      const uint32_t sel = (c & 3) | ((4 + (c & 3)) << 4);
+      const uint32_t b0 = __byte_perm(__byte_perm(src[0], src[1], sel), __byte_perm(src[2], src[3], sel), 0x5410);
+      const uint32_t b1 = __byte_perm(__byte_perm(src[4], src[5], sel), __byte_perm(src[6], src[7], sel), 0x5410);
       *reinterpret_cast<uint2*>(sm_vt + (lane * 8 + c) * kVRow + w * 8) = make_uint2(b0, b1);
     }
     __syncthreads();
@@ -342,11 +339,15 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
   float x[kQRowsPerWarp][8];
   int hh[kQRowsPerWarp], rr[kQRowsPerWarp];
   uint4 raw[kQRowsPerWarp];
+  // the padded row count is a multiple of 128, so the warp's four consecutive rows share a head:
+  // one 32-bit division per warp instead of two 64-bit ones per row
+  const int head0 = static_cast<int>(static_cast<unsigned>(item0 < total ? item0 : 0) / static_cast<unsigned>(mpad));
+  const int rowin0 = static_cast<int>(static_cast<unsigned>(item0 < total ? item0 : 0) - static_cast<unsigned>(head0) * static_cast<unsigned>(mpad));
 #pragma unroll
   for (int k = 0; k < kQRowsPerWarp; ++k) {
     const long long item = item0 + k;
-    hh[k] = static_cast<int>(item / mpad);
-    rr[k] = static_cast<int>(item % mpad);
+    hh[k] = head0;
+    rr[k] = rowin0 + k;
     if (item < total && rr[k] < g.T) {
       const uint16_t* src = reinterpret_cast<const uint16_t*>(g.q) +
                             (static_cast<size_t>(rr[k]) * g.Hq + hh[k]) * kD + lane * 8;
