@@ -427,10 +427,13 @@ def main():
     if any(w.status() != 0 for w in ws):
         raise SystemExit("device status word set: a bounded wait ran out; no number reported")
     t = torch.tensor([sec], device=dev, dtype=torch.float64)
+    t_min = t.clone()
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_min, op=dist.ReduceOp.MIN)
     sec_max = float(t.item())
     per_step = sec_max / args.steps
+    per_step_fastest_rank = float(t_min.item()) / args.steps
     total_flops = wl["flops_per_step"] * world
     value = total_flops / per_step / 1e12
 
@@ -483,7 +486,8 @@ def main():
                        "l2": "inputs larger than L2 (29.3 GB of pools, 3.2 GB of queries per step)"},
             "e2e": ({"value": e2e_value, "unit": "TF/s", "h2d_bytes_per_step": h2d_b, "d2h_bytes_per_step": d2h_b}
                     if e2e_value is not None else None),
-            "gpu_launches": KERNELS_PER_CALL * REQUESTS * LAYERS * args.steps,
+            "gpu_launches": KERNELS_PER_CALL * REQUESTS * LAYERS * args.steps * world,
+            "ms_per_step_fastest_rank": per_step_fastest_rank * 1e3,
             "clocks": clocks.summary(),
             "roofline": roofline,
             "cpu_baseline": cpu,
