@@ -134,11 +134,7 @@ __device__ __forceinline__ bool wait(const Ctx& c, int slot, uint32_t parity) {
   const uint32_t bar = c.bars + slot * 8;
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
-#ifdef AKL_TEST_WAIT
-    if (mbar_test_wait(bar, parity)) return true;
-#else
     if (mbar_try_wait(bar, parity)) return true;
-#endif
     if ((spin & 0xFFFu) == 0 && give_up(c, t0)) return false;
   }
 }

@@ -68,7 +68,7 @@ def _case(name, T, N, prefix, H, KVH, pool, dist, seed, *, rotate=True, center_k
 
 
 GOLDEN_CASES = [
-    # BASELINE config 1: 256 cached + 64 new, 24:4, 4096-slot pool, seeded permutation
+    # benchmark configuration 1 (the CPU-runnable case): 256 cached + 64 new, 24:4, 4096-slot pool, seeded permutation
     _case("c1_cpu_oracle", 64, 320, 256, 24, 4, "permuted", "outlier", object_seed(1),
           pool_rows=4096, sm_scale=1.0 / 16.0),
     # the reference's oracle-agreement shapes (tests/kernel/test_oracle_a.py:71-109)
@@ -149,7 +149,7 @@ def bitexact_inputs(meta: dict) -> dict:
 
 
 # --------------------------------------------------------------------------
-# BASELINE configurations (seeded stand-ins for the reference's synthetic schedule)
+# the benchmark configurations (seeded stand-ins for the reference's synthetic schedule)
 # --------------------------------------------------------------------------
 
 def c2_lengths(num_requests: int = 8, seed: int | None = None):

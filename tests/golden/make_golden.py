@@ -131,7 +131,7 @@ def extract_bitexact(ref_root: pathlib.Path) -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout (attn-kernel-lab)")
     args = ap.parse_args()
     ref_root = pathlib.Path(args.reference)
     torch.set_num_threads(max(1, torch.get_num_threads()))

@@ -251,7 +251,7 @@ def test_public_entry_equals_the_phase_calls_and_honours_out(pkg, cuda):
 
 
 def test_against_the_reference_output_fixture(pkg, cuda):
-    """BASELINE configuration 1 end to end against the output the reference's own oracle
+    """Benchmark configuration 1 end to end against the output the reference's own oracle
     produced (tests/golden/c1_cpu_oracle.npz): the kernels' reduction order differs from the
     reference's CPU library in the last place of a few means/scales, so this is the
     tolerance-level check (row-relative L2, the reference's own metric)."""
