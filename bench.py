@@ -482,6 +482,12 @@ def main():
                     "frac_of_2x_measured_bf16_sustained": achieved / (2.0 * peaks["bf16_tflops_sustained"]),
                     "frac_of_nominal_dense_fp8": achieved / NOMINAL_FP8_TFLOPS,
                     "attention_ms_per_launch": attn_ms, "flops_per_launch": attn_flops}
+        # secondary (HBM) roofline of the whole operator: one read of each input, one write of the
+        # output, per request-layer (2 N Hkv D 2 + 2 T Hq D 2 + N e_idx bytes), over the inclusive time
+        step_bytes = sum(2 * r["N"] * HKV * D * 2 + 2 * r["T"] * HQ * D * 2 + r["N"] * 8 for r in wl["reqs"]) * LAYERS
+        roofline["hbm_secondary"] = {"algorithmic_bytes_per_step": step_bytes,
+                                     "achieved": step_bytes / per_step / 1e9, "peak": peaks["hbm_gbs"],
+                                     "unit": "GB/s", "frac": step_bytes / per_step / 1e9 / peaks["hbm_gbs"]}
         if world == 1 and not args.no_cpu:
             dt, fl, _ = cpu_oracle_sample()
             cpu = {"value": fl / dt / 1e12, "unit": "TF/s", "cores": os.cpu_count(), "kind": "port",
