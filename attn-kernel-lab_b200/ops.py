@@ -322,9 +322,10 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Fa
     lse_out.  Every request is validated before the first launch.
 
     `workspace`: one workspace -> the requests run back to back on the current stream.
-    A list/tuple of K workspaces -> request i runs on side stream i % K with workspace i % K:
-    requests are independent units, so the gather/quantise kernels of one request fill the SMs
-    that the last wave of another request's attention kernel leaves idle.  The side streams fork
+    A list/tuple of K workspaces -> K side streams, one workspace each; the requests are dealt to
+    them longest first onto the least loaded stream (cost = attended pairs), so that the streams
+    finish together.  Requests are independent units, so the gather/quantise kernels of one
+    request fill the SMs that the last wave of another request's attention kernel leaves idle.  The side streams fork
     from the current stream and join it again before this function returns (event fork/join, so the
     whole batch can be captured in one CUDA graph); callers see ordinary stream semantics.
     Returns the list of results in request order."""
@@ -351,12 +352,21 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Fa
     sides = _streams_for(device, len(pool))
     fork = torch.cuda.Event()
     fork.record(main)
-    results = []
-    for k, side in enumerate(sides):
+    for side in sides:
         side.wait_event(fork)
-    for i, r in enumerate(requests):
-        with torch.cuda.stream(sides[i % len(pool)]):
-            results.append(run(r, pool[i % len(pool)]))
+    # longest-processing-time-first assignment of requests to streams
+    cost = [int(r["q"].shape[0]) * (int(r["prefix"]) + (int(r["q"].shape[0]) + 1) / 2.0) for r in requests]
+    load = [0.0] * len(pool)
+    lane_of = [0] * len(requests)
+    order = sorted(range(len(requests)), key=lambda i: (-cost[i], i))
+    for i in order:
+        k = min(range(len(pool)), key=lambda j: (load[j], j))
+        lane_of[i] = k
+        load[k] += cost[i]
+    results = [None] * len(requests)
+    for i in order:                      # each stream sees its requests longest first
+        with torch.cuda.stream(sides[lane_of[i]]):
+            results[i] = run(requests[i], pool[lane_of[i]])
     for side in sides:
         join = torch.cuda.Event()
         join.record(side)
