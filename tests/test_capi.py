@@ -32,6 +32,9 @@ def test_library_exports_every_declared_symbol(K):
         assert hasattr(lib, name), f"{name} is declared in include/akl.h but not exported"
     assert set(K.EXPORTS) <= set(names)
     assert lib.akl_abi_version() == int(re.search(r"#define AKL_ABI_VERSION (\d+)", HEADER).group(1))
+    from attn_kernel_lab_b200 import kernel as K
+    for name in ("AKL_FLAG_ROTATE", "AKL_FLAG_CENTER_K", "AKL_FLAG_QK_I8"):     # host constants == header
+        assert getattr(K, name) == int(re.search(rf"#define {name} (\d+)u", HEADER).group(1)), name
 
 
 def test_header_is_plain_c_with_reference_citations():
