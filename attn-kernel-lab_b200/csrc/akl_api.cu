@@ -67,6 +67,7 @@ int build_geom(const akl_call_t* c, Geom* g) {
   if (c->q_heads < 1 || c->kv_heads < 1 || c->q_heads % c->kv_heads) return AKL_ERR_UNSUPPORTED;
   if (c->kv_pos0 < 0 || c->kv_pos0 % kTile) return AKL_ERR_INVALID;
   if (!(c->sm_scale > 0.f)) return AKL_ERR_INVALID;
+  if (c->flags & ~(AKL_FLAG_ROTATE | AKL_FLAG_CENTER_K | AKL_FLAG_QK_I8)) return AKL_ERR_INVALID;   // unknown mode bit
   akl_ws_layout_t L;
   int rc = compute_layout(c->plan, &L);
   if (rc != AKL_OK) return rc;

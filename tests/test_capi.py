@@ -189,3 +189,50 @@ def test_logical_views_undo_the_swizzle(pkg):
     v8t[kvh, key // 128].view(-1)[d * 128 + ((((kk >> 4) ^ (d & 7)) << 4) | (kk & 15))] = 0x33
     vlog = ws.v8_logical(200)
     assert vlog.shape == (4, 256, 256) and int(vlog[kvh, key, d]) == 0x33 and int(vlog.sum()) == 0x33
+
+
+# ------------------------------------------------------------------ argument validation, host side only
+def _fake_call(K, **over):
+    """A call that would be valid if its pointers were real.  Every test below changes one field so
+    that validation refuses the call before anything is launched or dereferenced."""
+    lib = K.load()
+    plan = K.Plan(4096, 256, 24, 4)
+    lay = K.WsLayout()
+    assert lib.akl_workspace_layout(ctypes.byref(plan), ctypes.byref(lay)) == K.AKL_OK
+    c = K.Call()
+    c.q, c.k_pool, c.v_pool, c.idx, c.out = 0x10000, 0x20000, 0x30000, 0x40000, 0x50000
+    c.lse_out = None
+    c.workspace, c.workspace_bytes, c.plan = 0x100000, lay.total_bytes, plan
+    c.T, c.N, c.prefix, c.q_heads, c.kv_heads = 64, 320, 256, 24, 4
+    c.kv_dtype, c.idx_dtype = K.AKL_KV_BF16, K.AKL_IDX_I64
+    c.flags, c.sm_scale = K.AKL_FLAG_ROTATE | K.AKL_FLAG_CENTER_K, 1.0 / 16.0
+    c.kv_pos0 = c.n_total = c.tile0_global = c.ntiles_global = 0
+    for k, v in over.items():
+        setattr(c, k, v)
+    return lib, c
+
+
+@pytest.mark.parametrize("field, value, code", [
+    ("T", 0, "AKL_ERR_INVALID"),
+    ("N", 0, "AKL_ERR_INVALID"),
+    ("prefix", -1, "AKL_ERR_INVALID"),
+    ("kv_dtype", 7, "AKL_ERR_INVALID"),
+    ("idx_dtype", 5, "AKL_ERR_INVALID"),
+    ("sm_scale", 0.0, "AKL_ERR_INVALID"),
+    ("kv_pos0", 32, "AKL_ERR_INVALID"),              # a split starts on a 64-key tile boundary
+    ("flags", 8, "AKL_ERR_INVALID"),                 # unknown mode bit
+    ("workspace", None, "AKL_ERR_INVALID"),
+    ("kv_heads", 5, "AKL_ERR_UNSUPPORTED"),          # 24 q heads do not divide over 5
+    ("q_heads", 32, "AKL_ERR_CAPACITY"),             # not the head count the workspace was planned for
+    ("workspace_bytes", 4096, "AKL_ERR_CAPACITY"),
+    ("N", 4097, "AKL_ERR_CAPACITY"),                 # one key more than the plan's maximum tiles hold
+    ("T", 257, "AKL_ERR_CAPACITY"),
+    ("k_pool", 0x20008, "AKL_ERR_ALIGN"),
+    ("out", 0x50004, "AKL_ERR_ALIGN"),
+    ("workspace", 0x100200, "AKL_ERR_ALIGN"),        # 16-byte but not 1024-byte aligned
+])
+def test_native_entry_refuses_bad_arguments_before_any_launch(K, field, value, code):
+    lib, c = _fake_call(K, **{field: value})
+    for fn in ("akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_transform", "akl_attention"):
+        assert getattr(lib, fn)(ctypes.byref(c), None) == getattr(K, code), (fn, field)
+    assert lib.akl_strerror(getattr(K, code)).decode()
