@@ -8,9 +8,9 @@ native call (`akl_prefill_extend`, include/akl.h) that gathers, quantises, atten
 permute-copy (ops.py:597-609 of the reference).
 
 Differences a caller can see, all deliberate:
-  * `qk_i8` defaults to False (FP8 E4M3 QK, the mode this build is measured in); `qk_i8=True`
-    selects the reference's default INT8-QK mode (ops.py:496), an exact s32 QK^T on the same
-    tensor-core path.
+  * none in the QK operand type: `qk_i8` defaults to True as in the reference (ops.py:496), an
+    exact s32 QK^T on `tcgen05 kind::i8`; `qk_i8=False` is the FP8 E4M3 QK mode this build is
+    measured in (`kind::f8f6f4`).
   * `idx` may be int32 as well as int64 (the reference requires int64, ops.py:248-253).
   * `prefill_extend_batch` runs a list of requests back to back on one workspace.
 
@@ -251,7 +251,7 @@ def plan_workspace(device, *, max_kv_len: int, max_q_len: int, q_heads: int | No
 
 
 def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, lse_out=None,
-                   sm_scale=None, qk_i8: bool = False, rotate: bool = True, center_k: bool = True,
+                   sm_scale=None, qk_i8: bool = True, rotate: bool = True, center_k: bool = True,
                    return_lse: bool = False, capability: OperatorCapability = V1_CAPABILITY):
     """Bottom-right-causal paged EXTEND attention over a page-size-1 BF16/FP16 KV pool.
 
@@ -311,7 +311,7 @@ def _streams_for(device, count: int):
     return have[:count]
 
 
-def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = False, rotate: bool = True,
+def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = True, rotate: bool = True,
                          center_k: bool = True, return_lse: bool = False,
                          capability: OperatorCapability = V1_CAPABILITY):
     """Run a list of independent requests; results are exactly those of `prefill_extend` per

@@ -288,7 +288,7 @@ def _stream(device) -> int:
 
 
 def gather_quantize_kv(ws: FP8PrefillWorkspace, k_buffer, v_buffer, idx, need_vt8: bool = True,
-                       need_vb16: bool = False, center_k: bool = True, qk_i8: bool = False,
+                       need_vb16: bool = False, center_k: bool = True, qk_i8: bool = True,
                        rotate: bool = True) -> dict:
     """Gather + statistics + transform + quantise the request's K/V (quant.py:483-695).
 
@@ -313,7 +313,7 @@ def gather_quantize_kv(ws: FP8PrefillWorkspace, k_buffer, v_buffer, idx, need_vt
             "kmean": ws.view("kmean"), "vscale_t": ws.view("vst")[:, :nt], "n": n, "ntmax": nt}
 
 
-def quantize_q(ws: FP8PrefillWorkspace, q, sm_scale: float, qk_i8: bool = False,
+def quantize_q(ws: FP8PrefillWorkspace, q, sm_scale: float, qk_i8: bool = True,
                rotate: bool = True):
     """-> (q8 tile images, qscale [H, Mpad] f32 per row with sm_scale folded, Mpad)
     (quant.py:433-480).  `qk_i8`: INT8 bytes at amax/127 instead of E4M3 at amax/448."""

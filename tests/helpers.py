@@ -12,6 +12,18 @@ LOG2E = np.float32(1.4426950408889634)
 LOG2_448 = np.float32(8.807354922057604)
 
 
+def fp8_extend(pkg, *args, **kw):
+    """`prefill_extend` in the FP8-QK mode unless the caller names a mode (the operator's own
+    default is the reference's: INT8 QK)."""
+    kw.setdefault("qk_i8", False)
+    return pkg.prefill_extend(*args, **kw)
+
+
+def fp8_batch(pkg, *args, **kw):
+    kw.setdefault("qk_i8", False)
+    return pkg.prefill_extend_batch(*args, **kw)
+
+
 def bf16_ulp(x: np.ndarray) -> np.ndarray:
     """Spacing of bfloat16 at |x| (8 significand bits)."""
     return np.exp2(np.floor(np.log2(np.maximum(np.abs(x), 2.0 ** -126))) - 7)

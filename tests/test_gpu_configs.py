@@ -53,13 +53,13 @@ def test_gqa_sweep_fp16_pool_sixteen_ragged_requests(pkg, cuda, hq):
                      "cpu": (q, k, v)})
     max_n, max_t = max(p + t for p, t in lens), max(t for _, t in lens)
     wss = [pkg.plan_workspace(cuda, max_kv_len=max_n, max_q_len=max_t, q_heads=hq, kv_heads=4) for _ in range(4)]
-    pkg.prefill_extend_batch(reqs, workspace=wss, sm_scale=1 / 16, return_lse=True)
+    H.fp8_batch(pkg, reqs, workspace=wss, sm_scale=1 / 16, return_lse=True)
     torch.cuda.synchronize()
     assert all(ws.status() == 0 for ws in wss)
     batch = [(r["out"].clone(), r["lse_out"].clone()) for r in reqs]
     # one by one on a single workspace: the same bytes
     for r, (bo, bl) in zip(reqs, batch):
-        o, l = pkg.prefill_extend(r["q"], kp, vp, r["idx"], r["prefix"], workspace=wss[0], sm_scale=1 / 16,
+        o, l = H.fp8_extend(pkg, r["q"], kp, vp, r["idx"], r["prefix"], workspace=wss[0], sm_scale=1 / 16,
                                   return_lse=True)
         assert torch.equal(o, bo) and torch.equal(l, bl)
         assert torch.isfinite(o).all()
@@ -92,7 +92,7 @@ def test_long_request_split_in_eight_equals_unsplit(pkg, cuda):
     qd, idd = q.to(cuda), idx.to(cuda)
 
     ws = pkg.plan_workspace(cuda, max_kv_len=N, max_q_len=T, q_heads=Hq, kv_heads=KVH)
-    whole, whole_lse = pkg.prefill_extend(qd, kp, vp, idd, P, workspace=ws, sm_scale=1 / 16, return_lse=True)
+    whole, whole_lse = H.fp8_extend(pkg, qd, kp, vp, idd, P, workspace=ws, sm_scale=1 / 16, return_lse=True)
     torch.cuda.synchronize()
     assert ws.status() == 0
     kmean, vmean = ws.view("kmean").clone(), ws.view("vmean").clone()
@@ -162,7 +162,7 @@ def test_serving_batch_of_256_requests_replayed_from_one_graph(pkg, cuda):
            for _ in range(4)]
     ptrs = [w.buffer_pointers() for w in wss]
 
-    pkg.prefill_extend_batch(reqs, workspace=wss, sm_scale=1 / 16)            # eager (also warms the streams)
+    H.fp8_batch(pkg, reqs, workspace=wss, sm_scale=1 / 16)            # eager (also warms the streams)
     torch.cuda.synchronize()
     eager = out_all.clone()
     assert torch.isfinite(eager).all() and all(w.status() == 0 for w in wss)
@@ -172,7 +172,7 @@ def test_serving_batch_of_256_requests_replayed_from_one_graph(pkg, cuda):
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         with torch.cuda.graph(graph, stream=side):
-            pkg.prefill_extend_batch(reqs, workspace=wss, sm_scale=1 / 16)
+            H.fp8_batch(pkg, reqs, workspace=wss, sm_scale=1 / 16)
     torch.cuda.current_stream().wait_stream(side)
     out_all.fill_(float("nan"))
     graph.replay()
@@ -185,7 +185,7 @@ def test_serving_batch_of_256_requests_replayed_from_one_graph(pkg, cuda):
     graph.replay()
     torch.cuda.synchronize()
     replay2 = out_all.clone()
-    pkg.prefill_extend_batch(reqs, workspace=wss[0], sm_scale=1 / 16)
+    H.fp8_batch(pkg, reqs, workspace=wss[0], sm_scale=1 / 16)
     torch.cuda.synchronize()
     assert torch.equal(out_all.view(torch.int16), replay2.view(torch.int16))
     assert not torch.equal(replay2, eager)

@@ -101,7 +101,7 @@ def test_preprocessing_across_statistics_slabs(pkg, cuda):
     ws = pkg.FP8PrefillWorkspace(cuda)
     from attn_kernel_lab_b200 import quant
 
-    kvd = quant.gather_quantize_kv(ws, k.to(cuda), v.to(cuda), idx.to(cuda))
+    kvd = quant.gather_quantize_kv(ws, k.to(cuda), v.to(cuda), idx.to(cuda), qk_i8=False)
     torch.cuda.synchronize()
     assert kvd["n"] == n and kvd["ntmax"] == (n + 63) // 64
     kv = O.preprocess_kv(k[idx].float().numpy(), v[idx].float().numpy())
@@ -229,7 +229,7 @@ def test_attention_scores_probabilities_and_output(pkg, cuda, case, qk_i8):
 def _public(pkg, cuda, case, **kw):
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
-    return inp, (q, kp, vp, idx), pkg.prefill_extend(
+    return inp, (q, kp, vp, idx), H.fp8_extend(pkg, 
         q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"], rotate=case["rotate"],
         center_k=case["center_k"], capability=gen_cap(pkg, case), **kw)
 
@@ -242,10 +242,10 @@ def test_public_entry_equals_the_phase_calls_and_honours_out(pkg, cuda):
     assert torch.equal(out, out2) and torch.equal(lse, lse2)
     mine = torch.full_like(q, float("nan"))
     mine_lse = torch.full((case["T"], case["H"]), float("nan"), device=cuda)
-    res = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"], out=mine,
+    res = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"], out=mine,
                              lse_out=mine_lse, return_lse=True)
     assert res[0] is mine and res[1] is mine_lse and torch.equal(mine, out) and torch.equal(mine_lse, lse)
-    only = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"])
+    only = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"])
     assert isinstance(only, torch.Tensor) and torch.equal(only, out)      # LSE request does not move O
     assert out.shape == q.shape and out.dtype == torch.bfloat16 and lse.dtype == torch.float32
 
@@ -292,26 +292,26 @@ def test_capacity_equals_grow_and_reuse_after_a_larger_request(pkg, cuda):
     _, args_s, out_fresh = _public(pkg, cuda, small)
     ws = pkg.plan_workspace(cuda, max_kv_len=2048, max_q_len=512, q_heads=small["H"], kv_heads=4)
     before = ws.buffer_pointers()
-    out_cap = pkg.prefill_extend(*args_s, small["prefix"], sm_scale=small["sm_scale"], workspace=ws)
+    out_cap = H.fp8_extend(pkg, *args_s, small["prefix"], sm_scale=small["sm_scale"], workspace=ws)
     assert torch.equal(out_cap, out_fresh)
     # poison every scratch byte with the E4M3 NaN pattern, then rerun: nothing stale may be read
     ws._base.fill_(0x7F)
     ws.view("status").zero_()
-    out_again = pkg.prefill_extend(*args_s, small["prefix"], sm_scale=small["sm_scale"], workspace=ws)
+    out_again = H.fp8_extend(pkg, *args_s, small["prefix"], sm_scale=small["sm_scale"], workspace=ws)
     assert torch.equal(out_again, out_fresh) and ws.buffer_pointers() == before
     # grow-on-demand workspace reused after a larger request (stale longer data left behind)
     grow = pkg.FP8PrefillWorkspace(cuda)
     inp_l = cases.make_inputs(large)
     ql, kl, vl, il = H.to_dev(inp_l, cuda)
-    big1 = pkg.prefill_extend(ql, kl, vl, il, large["prefix"], sm_scale=large["sm_scale"], workspace=grow)
+    big1 = H.fp8_extend(pkg, ql, kl, vl, il, large["prefix"], sm_scale=large["sm_scale"], workspace=grow)
     small_on_24 = cases._case("s24", 37, 65, 28, 24, 4, "scattered", "uniform", 4101)
     inp_s = cases.make_inputs(small_on_24)
-    a = pkg.prefill_extend(*H.to_dev(inp_s, cuda), 28, workspace=grow)
-    b = pkg.prefill_extend(*H.to_dev(inp_s, cuda), 28)
+    a = H.fp8_extend(pkg, *H.to_dev(inp_s, cuda), 28, workspace=grow)
+    b = H.fp8_extend(pkg, *H.to_dev(inp_s, cuda), 28)
     assert torch.equal(a, b)
-    assert torch.equal(pkg.prefill_extend(ql, kl, vl, il, large["prefix"], sm_scale=large["sm_scale"], workspace=grow), big1)
+    assert torch.equal(H.fp8_extend(pkg, ql, kl, vl, il, large["prefix"], sm_scale=large["sm_scale"], workspace=grow), big1)
     with pytest.raises(pkg.WorkspaceCapacityError):
-        pkg.prefill_extend(ql, kl, vl, il, large["prefix"], workspace=pkg.plan_workspace(
+        H.fp8_extend(pkg, ql, kl, vl, il, large["prefix"], workspace=pkg.plan_workspace(
             cuda, max_kv_len=1000, max_q_len=512, q_heads=24, kv_heads=4))
 
 
@@ -320,8 +320,8 @@ def test_foreign_pool_slots_and_index_width_do_not_matter(pkg, cuda):
     case = cases.GOLDEN_CASES[3]                                   # scattered fp16 pool, 32:4
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
-    base = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"])
-    contiguous = pkg.prefill_extend(q, kp[idx].contiguous(), vp[idx].contiguous(),
+    base = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"])
+    contiguous = H.fp8_extend(pkg, q, kp[idx].contiguous(), vp[idx].contiguous(),
                                     torch.arange(case["N"], device=cuda), case["prefix"], sm_scale=case["sm_scale"])
     assert torch.equal(base, contiguous)
     mask = torch.ones(kp.shape[0], dtype=torch.bool, device=cuda)
@@ -329,8 +329,8 @@ def test_foreign_pool_slots_and_index_width_do_not_matter(pkg, cuda):
     kp2, vp2 = kp.clone(), vp.clone()
     kp2[mask] = float("nan")
     vp2[mask] = float("nan")
-    assert torch.equal(pkg.prefill_extend(q, kp2, vp2, idx, case["prefix"], sm_scale=case["sm_scale"]), base)
-    assert torch.equal(pkg.prefill_extend(q, kp, vp, idx.to(torch.int32), case["prefix"], sm_scale=case["sm_scale"]), base)
+    assert torch.equal(H.fp8_extend(pkg, q, kp2, vp2, idx, case["prefix"], sm_scale=case["sm_scale"]), base)
+    assert torch.equal(H.fp8_extend(pkg, q, kp, vp, idx.to(torch.int32), case["prefix"], sm_scale=case["sm_scale"]), base)
 
 
 def test_gqa_head_map_v_linearity_duplicate_channels_constant_v(pkg, cuda):
@@ -341,31 +341,31 @@ def test_gqa_head_map_v_linearity_duplicate_channels_constant_v(pkg, cuda):
     qg = q.clone()
     for grp in range(4):
         qg[:, grp * 6:(grp + 1) * 6] = q[:, grp * 6:grp * 6 + 1]
-    out = pkg.prefill_extend(qg, kp, vp, idx, case["prefix"])
+    out = H.fp8_extend(pkg, qg, kp, vp, idx, case["prefix"])
     for grp in range(4):
         for h in range(grp * 6 + 1, grp * 6 + 6):
             assert torch.equal(out[:, h], out[:, grp * 6])
     assert not torch.equal(out[:, 0], out[:, 6])
     # swapping kv heads 1 and 2 in the pool swaps the outputs of their query groups
     perm = [0, 2, 1, 3]
-    out_sw = pkg.prefill_extend(qg, kp[:, perm].contiguous(), vp[:, perm].contiguous(), idx, case["prefix"])
+    out_sw = H.fp8_extend(pkg, qg, kp[:, perm].contiguous(), vp[:, perm].contiguous(), idx, case["prefix"])
     assert torch.equal(out_sw[:, 0:6], out[:, 0:6])
     qsw = qg.clone()
     qsw[:, 6:12], qsw[:, 12:18] = qg[:, 12:18], qg[:, 6:12]
-    out_sw2 = pkg.prefill_extend(qsw, kp[:, perm].contiguous(), vp[:, perm].contiguous(), idx, case["prefix"])
+    out_sw2 = H.fp8_extend(pkg, qsw, kp[:, perm].contiguous(), vp[:, perm].contiguous(), idx, case["prefix"])
     assert torch.equal(out_sw2[:, 6:12], out[:, 12:18]) and torch.equal(out_sw2[:, 12:18], out[:, 6:12])
     # O(2V) == 2 O(V): a power-of-two scale moves no byte, only the scales
-    base = pkg.prefill_extend(q, kp, vp, idx, case["prefix"])
-    twice = pkg.prefill_extend(q, kp, (vp.float() * 2).to(vp.dtype), idx, case["prefix"])
+    base = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"])
+    twice = H.fp8_extend(pkg, q, kp, (vp.float() * 2).to(vp.dtype), idx, case["prefix"])
     assert torch.equal(twice.float(), base.float() * 2)
     # duplicated V channels give identical output channels
     vd = vp.clone()
     vd[:, :, 128:] = vd[:, :, :128]
-    dup = pkg.prefill_extend(q, kp, vd, idx, case["prefix"])
+    dup = H.fp8_extend(pkg, q, kp, vd, idx, case["prefix"])
     assert torch.equal(dup[:, :, 128:], dup[:, :, :128])
     # constant V: centred V is zero, the output is the mean, exactly
     vc = torch.full_like(vp, 0.375)
-    const = pkg.prefill_extend(q, kp, vc, idx, case["prefix"])
+    const = H.fp8_extend(pkg, q, kp, vc, idx, case["prefix"])
     assert bool((const == 0.375).all())
 
 
@@ -374,7 +374,7 @@ def test_determinism_and_stream_semantics(pkg, cuda):
     inp = cases.make_inputs(case)
     q, kp, vp, idx = H.to_dev(inp, cuda)
     ws = pkg.plan_workspace(cuda, max_kv_len=case["N"], max_q_len=case["T"], q_heads=24, kv_heads=4)
-    a = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], workspace=ws)
+    a = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], workspace=ws)
     outs = [torch.empty_like(q) for _ in range(3)]
     torch.cuda.synchronize()
     torch.cuda.set_sync_debug_mode("error")             # steady state must not synchronise
@@ -382,7 +382,7 @@ def test_determinism_and_stream_semantics(pkg, cuda):
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
             for o in outs:
-                pkg.prefill_extend(q, kp, vp, idx, case["prefix"], workspace=ws, out=o)
+                H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], workspace=ws, out=o)
     finally:
         torch.cuda.set_sync_debug_mode("default")
     side.synchronize()
@@ -400,17 +400,17 @@ def test_cuda_graph_capture_replay_changed_values_and_poisoned_scratch(pkg, cuda
     ws = pkg.plan_workspace(cuda, max_kv_len=1200, max_q_len=256, q_heads=24, kv_heads=4)
     out = torch.empty_like(q)
     lse = torch.empty((case["T"], 24), dtype=torch.float32, device=cuda)
-    eager = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], workspace=ws, return_lse=True)
+    eager = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], workspace=ws, return_lse=True)
     eager = (eager[0].clone(), eager[1].clone())
     ptrs = ws.buffer_pointers()
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        pkg.prefill_extend(q, kp, vp, idx, case["prefix"], workspace=ws, out=out, lse_out=lse, return_lse=True)
+        H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], workspace=ws, out=out, lse_out=lse, return_lse=True)
     torch.cuda.current_stream().wait_stream(side)
     with torch.cuda.graph(graph):
-        pkg.prefill_extend(q, kp, vp, idx, case["prefix"], workspace=ws, out=out, lse_out=lse, return_lse=True)
+        H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], workspace=ws, out=out, lse_out=lse, return_lse=True)
     out.fill_(float("nan"))
     lse.fill_(float("nan"))
     graph.replay()
@@ -422,7 +422,7 @@ def test_cuda_graph_capture_replay_changed_values_and_poisoned_scratch(pkg, cuda
     vp.copy_((vp.float() * -1.5).to(vp.dtype))
     graph.replay()
     torch.cuda.synchronize()
-    fresh = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], return_lse=True)
+    fresh = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], return_lse=True)
     assert torch.equal(out, fresh[0]) and torch.equal(lse, fresh[1])
     # scratch poisoned with the E4M3 NaN byte between replays
     for name in ("k8", "v8t", "q8"):
@@ -443,15 +443,15 @@ def test_batch_over_streams_equals_one_by_one_and_can_be_captured(pkg, cuda):
         q, kp, vp, idx = H.to_dev(inp, cuda)
         reqs.append({"q": q, "k_pool": kp, "v_pool": vp, "idx": idx, "prefix": p,
                      "out": torch.empty_like(q), "lse_out": torch.empty((t, 24), dtype=torch.float32, device=cuda)})
-        single.append(pkg.prefill_extend(q, kp, vp, idx, p, return_lse=True))
+        single.append(H.fp8_extend(pkg, q, kp, vp, idx, p, return_lse=True))
     wss = [pkg.plan_workspace(cuda, max_kv_len=1200, max_q_len=256, q_heads=24, kv_heads=4) for _ in range(2)]
-    res = pkg.prefill_extend_batch(reqs, workspace=wss, return_lse=True)
+    res = H.fp8_batch(pkg, reqs, workspace=wss, return_lse=True)
     torch.cuda.synchronize()
     for (o, l), (so, sl), r in zip(res, single, reqs):
         assert o is r["out"] and torch.equal(o, so) and torch.equal(l, sl)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        pkg.prefill_extend_batch(reqs, workspace=wss, return_lse=True)
+        H.fp8_batch(pkg, reqs, workspace=wss, return_lse=True)
     for r in reqs:
         r["out"].fill_(float("nan"))
     graph.replay()
@@ -478,14 +478,14 @@ def test_main_profile_shape_sampled_oracle_and_properties(pkg, cuda):
     kp[idx], vp[idx] = k, v
     qd, kd, vd, idd = q.to(cuda), kp.to(cuda), vp.to(cuda), idx.to(cuda)
     ws = pkg.plan_workspace(cuda, max_kv_len=N, max_q_len=T, q_heads=Hq, kv_heads=KVH)
-    out, lse = pkg.prefill_extend(qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws, return_lse=True)
+    out, lse = H.fp8_extend(pkg, qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws, return_lse=True)
     out, lse = out.clone(), lse.clone()
-    assert torch.equal(pkg.prefill_extend(qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws), out)
-    assert torch.equal(pkg.prefill_extend(qd, k.to(cuda), v.to(cuda), torch.arange(N, device=cuda), P,
+    assert torch.equal(H.fp8_extend(pkg, qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws), out)
+    assert torch.equal(H.fp8_extend(pkg, qd, k.to(cuda), v.to(cuda), torch.arange(N, device=cuda), P,
                                           sm_scale=1 / 16, workspace=ws), out)
-    twice = pkg.prefill_extend(qd, kd, (vd.float() * 2).to(torch.bfloat16), idd, P, sm_scale=1 / 16, workspace=ws)
+    twice = H.fp8_extend(pkg, qd, kd, (vd.float() * 2).to(torch.bfloat16), idd, P, sm_scale=1 / 16, workspace=ws)
     assert torch.equal(twice.float(), out.float() * 2)
-    pkg.prefill_extend(qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws)
+    H.fp8_extend(pkg, qd, kd, vd, idd, P, sm_scale=1 / 16, workspace=ws)
     torch.cuda.synchronize()
     assert ws.status() == 0
     qp, kv = H.workspace_packs(ws, T, N)
@@ -561,5 +561,5 @@ def test_kv_axis_split_emulated_on_one_gpu(pkg, cuda):
     assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.95
     assert np.abs(mlse.cpu().numpy() - want_l).max() < 5e-3
     # distance to the unsplit operator, reported by the split oracle test: same LSE, P-noise apart
-    single = pkg.prefill_extend(q, kp, vp, idx, prefix, sm_scale=case["sm_scale"], return_lse=True)
+    single = H.fp8_extend(pkg, q, kp, vp, idx, prefix, sm_scale=case["sm_scale"], return_lse=True)
     assert np.abs(single[1].cpu().numpy() - mlse.cpu().numpy()).max() < 5e-3

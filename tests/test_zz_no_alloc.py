@@ -14,6 +14,7 @@ import pytest
 import torch
 
 import cases
+import helpers
 
 pytestmark = pytest.mark.gpu
 
@@ -25,7 +26,7 @@ def _run_both(pkg, cuda, case):
     inp = cases.make_inputs(case)
     q, kp, vp, idx = (inp[k].to(cuda) for k in ("q", "k_pool", "v_pool", "idx"))
     T, H, N, KVH = case["T"], case["H"], case["N"], case["KVH"]
-    ref_out, ref_lse = pkg.prefill_extend(q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"],
+    ref_out, ref_lse = helpers.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], sm_scale=case["sm_scale"],
                                           rotate=case["rotate"], center_k=case["center_k"], return_lse=True)
     out = torch.full_like(q, float("nan"))
     lse = torch.full((T, H), float("nan"), dtype=torch.float32, device=cuda)
