@@ -75,9 +75,18 @@ int build_geom(const akl_call_t* c, Geom* g) {
   if (c->q_heads != c->plan.q_heads || c->kv_heads != c->plan.kv_heads) return AKL_ERR_CAPACITY;
   const int nt = (c->N + kTile - 1) / kTile;
   const int mtiles = (c->T + kQTile - 1) / kQTile;
-  const int ntg = c->ntiles_global > 0 ? c->ntiles_global : nt;
-  if (nt > L.ntiles || mtiles > L.mtiles || ntg > L.ntiles || c->tile0_global + nt > L.ntiles)
-    return AKL_ERR_CAPACITY;
+  // KV-axis split fields: the first local tile's global index must be the one kv_pos0 names,
+  // the local tiles must lie inside the global tile range, and the global length must cover
+  // this call's positions (all compared in 64 bits: the fields come from a foreign caller)
+  if (c->tile0_global < 0 || c->ntiles_global < 0 || c->n_total < 0) return AKL_ERR_INVALID;
+  if (static_cast<int64_t>(c->tile0_global) * kTile != static_cast<int64_t>(c->kv_pos0)) return AKL_ERR_INVALID;
+  const int64_t last_tile = static_cast<int64_t>(c->tile0_global) + nt;
+  const int64_t ntg64 = c->ntiles_global > 0 ? c->ntiles_global : last_tile;
+  if (ntg64 < last_tile) return AKL_ERR_INVALID;
+  if (c->n_total > 0 && static_cast<int64_t>(c->n_total) < static_cast<int64_t>(c->kv_pos0) + c->N) return AKL_ERR_INVALID;
+  if (c->n_total == 0 && c->kv_pos0 != 0) return AKL_ERR_INVALID;   // a split must state the global length
+  if (nt > L.ntiles || mtiles > L.mtiles || ntg64 > L.ntiles) return AKL_ERR_CAPACITY;
+  const int ntg = static_cast<int>(ntg64);
   const uintptr_t mask = reinterpret_cast<uintptr_t>(c->workspace) | reinterpret_cast<uintptr_t>(c->k_pool) |
                          reinterpret_cast<uintptr_t>(c->v_pool) | reinterpret_cast<uintptr_t>(c->q) |
                          reinterpret_cast<uintptr_t>(c->out);

@@ -230,9 +230,30 @@ def _fake_call(K, **over):
     ("k_pool", 0x20008, "AKL_ERR_ALIGN"),
     ("out", 0x50004, "AKL_ERR_ALIGN"),
     ("workspace", 0x100200, "AKL_ERR_ALIGN"),        # 16-byte but not 1024-byte aligned
+    ("tile0_global", -1, "AKL_ERR_INVALID"),         # would index the tile-sum arrays before their start
+    ("tile0_global", 2, "AKL_ERR_INVALID"),          # disagrees with kv_pos0 = 0
+    ("ntiles_global", -3, "AKL_ERR_INVALID"),
+    ("n_total", -5, "AKL_ERR_INVALID"),
+    ("n_total", 319, "AKL_ERR_INVALID"),             # global length shorter than this call's positions
 ])
 def test_native_entry_refuses_bad_arguments_before_any_launch(K, field, value, code):
     lib, c = _fake_call(K, **{field: value})
     for fn in ("akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_transform", "akl_attention"):
         assert getattr(lib, fn)(ctypes.byref(c), None) == getattr(K, code), (fn, field)
     assert lib.akl_strerror(getattr(K, code)).decode()
+
+
+@pytest.mark.parametrize("over, code", [
+    (dict(kv_pos0=64, tile0_global=1, n_total=0, ntiles_global=6), "AKL_ERR_INVALID"),  # split without a global length
+    (dict(kv_pos0=64, tile0_global=0x7FFFFFF0, n_total=384, ntiles_global=6), "AKL_ERR_INVALID"),  # int overflow bait
+    (dict(kv_pos0=64, tile0_global=1, n_total=384, ntiles_global=5), "AKL_ERR_INVALID"),  # written tiles beyond the global range
+    (dict(kv_pos0=64, tile0_global=1, n_total=383, ntiles_global=6), "AKL_ERR_INVALID"),  # divisor smaller than kv_pos0 + N
+    (dict(kv_pos0=64, tile0_global=1, n_total=8192, ntiles_global=128), "AKL_ERR_CAPACITY"),  # more global tiles than the plan
+])
+def test_kv_split_fields_are_checked_together_on_the_host(K, over, code):
+    """The phase entry points take the KV-axis split fields; an inconsistent combination must be
+    refused before any launch (a negative or overflowing tile index would be an out-of-bounds
+    device store).  The consistent combinations run in the GPU split tests."""
+    lib, c = _fake_call(K, **over)
+    for fn in ("akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales", "akl_kv_transform", "akl_attention"):
+        assert getattr(lib, fn)(ctypes.byref(c), None) == getattr(K, code), (fn, over)
