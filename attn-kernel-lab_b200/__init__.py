@@ -14,14 +14,17 @@ from .capability import (
     check_supported,
 )
 from .kernel import NativeError, build, load, source_build_id
-from .ops import PrefillRequest, check_request, plan_workspace, prefill_extend, prefill_extend_batch
+from .ops import (PrefillRequest, check_request, plan_batch_workspace, plan_workspace, prefill_extend,
+                  prefill_extend_batch)
 from .paged import fp8_paged_prefill
-from .quant import CapacityPlan, FP8PrefillWorkspace, WorkspaceCapacityError
+from .quant import (BatchPlan, CapacityPlan, FP8PrefillBatchWorkspace, FP8PrefillWorkspace,
+                    WorkspaceCapacityError)
 
 __all__ = [
     "CapabilityError", "GENERALIZATION_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
     "check_supported", "NativeError", "build", "load", "source_build_id", "PrefillRequest",
-    "check_request", "plan_workspace", "prefill_extend", "prefill_extend_batch", "CapacityPlan",
+    "check_request", "plan_workspace", "plan_batch_workspace", "prefill_extend", "prefill_extend_batch",
+    "CapacityPlan", "BatchPlan", "FP8PrefillBatchWorkspace",
     "FP8PrefillWorkspace", "WorkspaceCapacityError", "BackendSettings", "make_backend_class", "fp8_paged_prefill",
 ]
 

@@ -1,8 +1,11 @@
 // C ABI of libakl_sm100a.so (declared in include/akl.h): argument checking, workspace
 // geometry, and the phase sequence of one request.  No device allocation, no stream
 // synchronisation, no exceptions across the boundary.
+#include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "akl_common.cuh"
 
@@ -126,6 +129,105 @@ int build_geom(const akl_call_t* c, Geom* g) {
   return AKL_OK;
 }
 
+// ---- batched entry: geometry of the shared workspace and of the request table ----------
+struct BatchLayout {
+  uint64_t ws_bytes, table_bytes;
+  uint64_t off_q8, off_qscale, off_k8, off_v8t, off_kscale, off_vst, off_vlog2r, off_vinvr, off_vam,
+      off_vscale, off_vsmax, off_kmean, off_vmean, off_ktsum, off_vtsum, off_vtmax, off_vtmin, off_status;
+  uint32_t t_geoms, t_stat_off, t_qcta_off, t_items;
+};
+
+constexpr int kQRowsPerCtaHost = 32;   // rows one Q-quantisation CTA covers (8 warps x 4 rows)
+
+int compute_batch_layout(const akl_batch_caps_t& c, BatchLayout* o) {
+  if (c.max_requests < 1 || c.max_total_kv_pairs < 1 || c.max_total_q_tiles < 1 || c.q_heads < 1 || c.kv_heads < 1)
+    return AKL_ERR_INVALID;
+  if (c.q_heads % c.kv_heads) return AKL_ERR_UNSUPPORTED;
+  // flat item indices are 32-bit in the kernels
+  const uint64_t R = c.max_requests, P = c.max_total_kv_pairs, NT = 2 * P, MT = c.max_total_q_tiles;
+  const uint64_t hq = c.q_heads, hkv = c.kv_heads;
+  if (R > (1u << 20) || 2 * NT * hkv >= (1ull << 31) || MT * hq * (kQTile / kQRowsPerCtaHost) >= (1ull << 31) ||
+      hq >= (1u << 15))
+    return AKL_ERR_UNSUPPORTED;
+  std::memset(o, 0, sizeof(*o));
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) {
+    const uint64_t at = off;
+    off = align_up(off + bytes, 1024);
+    return at;
+  };
+  o->off_q8 = take(hq * MT * kImageBytes);
+  o->off_qscale = take(hq * MT * kQTile * 4);
+  o->off_k8 = take(hkv * P * kImageBytes);
+  o->off_v8t = take(hkv * P * kImageBytes);
+  o->off_kscale = take(hkv * NT * 4);
+  o->off_vst = take(hkv * NT * 4);
+  o->off_vlog2r = take(hkv * NT * 4);
+  o->off_vinvr = take(hkv * NT * 4);
+  o->off_vam = take(hkv * NT * 4);
+  o->off_vscale = take(R * hkv * 4);
+  o->off_vsmax = take(R * hkv * 4);
+  o->off_kmean = take(R * hkv * kD * 4);
+  o->off_vmean = take(R * hkv * kD * 4);
+  o->off_ktsum = take(hkv * NT * kD * 4);
+  o->off_vtsum = take(hkv * NT * kD * 4);
+  o->off_vtmax = take(hkv * NT * kD * 4);
+  o->off_vtmin = take(hkv * NT * kD * 4);
+  o->off_status = take(256);
+  o->ws_bytes = off;
+  uint64_t t = sizeof(BatchHeader);
+  o->t_geoms = static_cast<uint32_t>(t);
+  t = align_up(t + R * sizeof(Geom), 16);
+  o->t_stat_off = static_cast<uint32_t>(t);
+  t = align_up(t + (R + 1) * 4, 16);
+  o->t_qcta_off = static_cast<uint32_t>(t);
+  t = align_up(t + (R + 1) * 4, 16);
+  o->t_items = static_cast<uint32_t>(t);
+  t = align_up(t + MT * hq * 8, 16);
+  if (t >= (1ull << 32)) return AKL_ERR_UNSUPPORTED;
+  o->table_bytes = t;
+  return AKL_OK;
+}
+
+int check_batch(const akl_batch_t* b, BatchLayout* L) {
+  if (b == nullptr || b->workspace == nullptr) return AKL_ERR_INVALID;
+  if (b->kv_dtype != AKL_KV_BF16 && b->kv_dtype != AKL_KV_FP16) return AKL_ERR_INVALID;
+  if (b->idx_dtype != AKL_IDX_I64 && b->idx_dtype != AKL_IDX_I32) return AKL_ERR_INVALID;
+  if (!(b->sm_scale > 0.f)) return AKL_ERR_INVALID;
+  if (b->flags & ~(AKL_FLAG_ROTATE | AKL_FLAG_CENTER_K | AKL_FLAG_QK_I8)) return AKL_ERR_INVALID;
+  int rc = compute_batch_layout(b->caps, L);
+  if (rc != AKL_OK) return rc;
+  if (b->workspace_bytes < L->ws_bytes || b->table_bytes < L->table_bytes) return AKL_ERR_CAPACITY;
+  if (reinterpret_cast<uintptr_t>(b->workspace) & 1023u) return AKL_ERR_ALIGN;
+  return AKL_OK;
+}
+
+BatchRef make_ref(const akl_batch_t* b, const BatchLayout& L, void* table) {
+  BatchRef r;
+  r.table = static_cast<uint8_t*>(table);
+  r.off_geoms = L.t_geoms;
+  r.off_stat_off = L.t_stat_off;
+  r.off_qcta_off = L.t_qcta_off;
+  r.off_items = L.t_items;
+  r.max_requests = b->caps.max_requests;
+  return r;
+}
+
+int device_sm_count(int* out) {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { note_cuda_error(e, "cudaGetDevice"); return AKL_ERR_CUDA; }
+  int n = (dev >= 0 && dev < 64) ? cached[dev].load(std::memory_order_relaxed) : 0;
+  if (n == 0) {
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || n < 1) { note_cuda_error(e, "cudaDeviceGetAttribute(SM count)"); return AKL_ERR_CUDA; }
+    if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
+  }
+  *out = n;
+  return AKL_OK;
+}
+
 int need_q(const akl_call_t* c) { return (c->q == nullptr) ? AKL_ERR_INVALID : AKL_OK; }
 int need_out(const akl_call_t* c) { return (c->out == nullptr) ? AKL_ERR_INVALID : AKL_OK; }
 
@@ -227,6 +329,133 @@ int akl_prefill_extend(const akl_call_t* c, void* stream) {
   if ((rc = launch_kv_means(g, s, /*fuse_scales=*/true)) != AKL_OK) return rc;
   if ((rc = launch_kv_transform(g, c->kv_dtype, c->idx_dtype, s)) != AKL_OK) return rc;
   return launch_attention(g, s);
+}
+
+int akl_batch_layout(const akl_batch_caps_t* caps, akl_batch_layout_t* out) {
+  if (caps == nullptr || out == nullptr) return AKL_ERR_INVALID;
+  BatchLayout L;
+  int rc = compute_batch_layout(*caps, &L);
+  if (rc != AKL_OK) return rc;
+  std::memset(out, 0, sizeof(*out));
+  out->workspace_bytes = L.ws_bytes;
+  out->table_bytes = L.table_bytes;
+  out->ws_off_status = L.off_status;
+  out->table_off_geoms = L.t_geoms;
+  out->table_geom_stride = static_cast<uint32_t>(sizeof(Geom));
+  out->table_off_stat_totals = L.t_stat_off;
+  out->table_off_qcta_totals = L.t_qcta_off;
+  out->table_off_items = L.t_items;
+  return AKL_OK;
+}
+
+int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* reqs, int32_t n, void* table_host) {
+  BatchLayout L;
+  int rc = check_batch(b, &L);
+  if (rc != AKL_OK) return rc;
+  if (table_host == nullptr || n < 0 || (n > 0 && reqs == nullptr)) return AKL_ERR_INVALID;
+  if (n > b->caps.max_requests) return AKL_ERR_CAPACITY;
+  const int hq = b->caps.q_heads, hkv = b->caps.kv_heads;
+  const int64_t P = b->caps.max_total_kv_pairs, MT = b->caps.max_total_q_tiles;
+  uint8_t* tab = static_cast<uint8_t*>(table_host);
+  uint8_t* ws = static_cast<uint8_t*>(b->workspace);
+  Geom* geoms = reinterpret_cast<Geom*>(tab + L.t_geoms);
+  int32_t* stat_off = reinterpret_cast<int32_t*>(tab + L.t_stat_off);
+  int32_t* qcta_off = reinterpret_cast<int32_t*>(tab + L.t_qcta_off);
+  int32_t* items = reinterpret_cast<int32_t*>(tab + L.t_items);
+
+  int64_t pair_off = 0, mtile_off = 0, stat_items = 0, q_ctas = 0;
+  std::vector<double> req_cost(static_cast<size_t>(n), 0.0);
+  for (int r = 0; r < n; ++r) {
+    const akl_batch_request_t& q = reqs[r];
+    if (q.q == nullptr || q.k_pool == nullptr || q.v_pool == nullptr || q.idx == nullptr || q.out == nullptr)
+      return AKL_ERR_INVALID;
+    if (q.T < 1 || q.N < 1 || q.prefix < 0 || q.prefix > q.N - q.T) return AKL_ERR_INVALID;
+    const uintptr_t mask = reinterpret_cast<uintptr_t>(q.q) | reinterpret_cast<uintptr_t>(q.k_pool) |
+                           reinterpret_cast<uintptr_t>(q.v_pool) | reinterpret_cast<uintptr_t>(q.out);
+    if (mask & 15u) return AKL_ERR_ALIGN;
+    const int64_t npairs = (static_cast<int64_t>(q.N) + kPair - 1) / kPair;
+    const int64_t nt = (static_cast<int64_t>(q.N) + kTile - 1) / kTile;
+    const int64_t mtiles = (static_cast<int64_t>(q.T) + kQTile - 1) / kQTile;
+    if (pair_off + npairs > P || mtile_off + mtiles > MT || mtiles >= (1 << 16)) return AKL_ERR_CAPACITY;
+    const int64_t tile_off = 2 * pair_off;
+    Geom& g = geoms[r];
+    std::memset(&g, 0, sizeof(g));
+    g.q = q.q; g.k_pool = q.k_pool; g.v_pool = q.v_pool; g.idx = q.idx; g.out = q.out; g.lse_out = q.lse_out;
+    g.q8 = ws + L.off_q8 + mtile_off * kImageBytes;
+    g.qscale = reinterpret_cast<float*>(ws + L.off_qscale) + mtile_off * kQTile;
+    g.k8 = ws + L.off_k8 + pair_off * kImageBytes;
+    g.v8t = ws + L.off_v8t + pair_off * kImageBytes;
+    g.kscale = reinterpret_cast<float*>(ws + L.off_kscale) + tile_off;
+    g.vst = reinterpret_cast<float*>(ws + L.off_vst) + tile_off;
+    g.vlog2r = reinterpret_cast<float*>(ws + L.off_vlog2r) + tile_off;
+    g.vinvr = reinterpret_cast<float*>(ws + L.off_vinvr) + tile_off;
+    g.vam = reinterpret_cast<float*>(ws + L.off_vam) + tile_off;
+    g.vscale = reinterpret_cast<float*>(ws + L.off_vscale) + static_cast<int64_t>(r) * hkv;
+    g.vsmax = reinterpret_cast<float*>(ws + L.off_vsmax) + static_cast<int64_t>(r) * hkv;
+    g.kmean = reinterpret_cast<float*>(ws + L.off_kmean) + static_cast<int64_t>(r) * hkv * kD;
+    g.vmean = reinterpret_cast<float*>(ws + L.off_vmean) + static_cast<int64_t>(r) * hkv * kD;
+    g.ktsum = reinterpret_cast<float*>(ws + L.off_ktsum) + tile_off * hkv * kD;
+    g.vtsum = reinterpret_cast<float*>(ws + L.off_vtsum) + tile_off * hkv * kD;
+    g.vtmax = reinterpret_cast<float*>(ws + L.off_vtmax) + tile_off * kD;
+    g.vtmin = reinterpret_cast<float*>(ws + L.off_vtmin) + tile_off * kD;
+    g.status = reinterpret_cast<int*>(ws + L.off_status);
+    g.T = q.T; g.N = q.N; g.prefix = q.prefix; g.Hq = hq; g.Hkv = hkv;
+    g.npairs_cap = static_cast<int>(P); g.ntiles_cap = static_cast<int>(2 * P); g.mtiles_cap = static_cast<int>(MT);
+    g.nt = static_cast<int>(nt); g.mtiles = static_cast<int>(mtiles);
+    g.kv_pos0 = 0; g.n_total = q.N; g.tile0_global = 0; g.ntiles_global = static_cast<int>(nt);
+    g.flags = b->flags; g.sm_scale = b->sm_scale;
+    stat_off[r] = static_cast<int32_t>(stat_items);
+    qcta_off[r] = static_cast<int32_t>(q_ctas);
+    stat_items += nt * hkv;
+    q_ctas += static_cast<int64_t>(hq) * mtiles * kQTile / kQRowsPerCtaHost;
+    pair_off += npairs;
+    mtile_off += mtiles;
+    req_cost[r] = static_cast<double>(q.T) * (q.prefix + (q.T + 1) / 2.0);
+  }
+  stat_off[n] = static_cast<int32_t>(stat_items);
+  qcta_off[n] = static_cast<int32_t>(q_ctas);
+  for (int r = n + 1; r <= b->caps.max_requests; ++r) { stat_off[r] = stat_off[n]; qcta_off[r] = qcta_off[n]; }
+
+  // attention work items: requests longest first (so the K/V tiles of one or two requests stay in
+  // L2 while their items run), inside a request the deepest query tiles first, heads together
+  std::vector<int> order(static_cast<size_t>(n));
+  for (int r = 0; r < n; ++r) order[r] = r;
+  std::stable_sort(order.begin(), order.end(), [&](int a, int c) { return req_cost[a] > req_cost[c]; });
+  int64_t n_items = 0;
+  for (int r : order) {
+    const Geom& g = geoms[r];
+    for (int qt = g.mtiles - 1; qt >= 0; --qt)
+      for (int h = 0; h < hq; ++h) {
+        items[2 * n_items] = r;
+        items[2 * n_items + 1] = (h << 16) | qt;
+        ++n_items;
+      }
+  }
+  BatchHeader* hdr = reinterpret_cast<BatchHeader*>(tab);
+  std::memset(hdr, 0, sizeof(*hdr));
+  hdr->magic = kBatchMagic;
+  hdr->n_requests = n;
+  hdr->n_stat_items = static_cast<int32_t>(stat_items);
+  hdr->n_q_ctas = static_cast<int32_t>(q_ctas);
+  hdr->n_attn_items = static_cast<int32_t>(n_items);
+  hdr->attn_counter = 0;
+  return AKL_OK;
+}
+
+int akl_prefill_extend_batch(const akl_batch_t* b, void* stream) {
+  BatchLayout L;
+  int rc = check_batch(b, &L);
+  if (rc != AKL_OK) return rc;
+  if (b->table == nullptr) return AKL_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(b->table) & 15u) return AKL_ERR_ALIGN;
+  int sms = 0;
+  if ((rc = device_sm_count(&sms)) != AKL_OK) return rc;
+  const BatchRef ref = make_ref(b, L, b->table);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if ((rc = launch_batch_stats(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
+  if ((rc = launch_batch_means(ref, b->caps.kv_heads, s)) != AKL_OK) return rc;
+  if ((rc = launch_batch_transform(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
+  return launch_batch_attention(ref, (b->flags & AKL_FLAG_QK_I8) != 0, sms, s);
 }
 
 int akl_merge_states(const akl_merge_t* m, void* stream) {

@@ -39,6 +39,7 @@
 // 384-511.  QK^T runs at N = 128 keys per MMA group, softmax and PV at the operator's 64-key
 // tile granularity (two K=32 MMAs of N = 256 per tile).
 #include <atomic>
+#include <cstring>
 
 #include "akl_common.cuh"
 #include "akl_sm100_ptx.cuh"
@@ -190,32 +191,61 @@ __device__ __forceinline__ float acc_value(uint32_t word) {
   return kI8 ? __int2float_rn(static_cast<int>(word)) : __uint_as_float(word);
 }
 
-template <bool kDump, bool kI8>
-__global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
+// kBatch = false: one work item per CTA, (q tile, head) from the block index, geometry in the
+// kernel parameter.  kBatch = true: a persistent CTA draws (request, head, q tile) items from the
+// request table's list through an atomic counter and keeps the current request's geometry in
+// shared memory; tensor memory is allocated once, the mbarriers are rebuilt per item.
+template <bool kDump, bool kI8, bool kBatch>
+__global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_constant__ Geom g_param, BatchRef bref) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int sm_item;
+  __shared__ Geom sm_geom;
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
   float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
   float2* sm_fin = reinterpret_cast<float2*>(smem_gen + kOffFin);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
-  const int h = blockIdx.y;
-  const int kvh = h / (g.Hq / g.Hkv);
-  const int m0 = qt * kQTile;
+  const Geom& g = kBatch ? sm_geom : g_param;
 
-  // keys this CTA visits, in local (this call's) positions
-  long long hi_ll = static_cast<long long>(g.prefix) + m0 + kQTile - g.kv_pos0;
-  const int hi = static_cast<int>(hi_ll < 0 ? 0 : (hi_ll > g.N ? g.N : hi_ll));
-  const int ntile = (hi + kTile - 1) / kTile;
-  const int npair = (ntile + 1) / 2;
+  if (tid == 0) abort_flag = 0;
+  if (warp == kProducerWarp) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  int cur_request = -1;
 
-  Ctx ctx{smem + kOffBar, g.status, &abort_flag};
+  for (int iter = 0;; ++iter) {
+  int qt, h;
+  if (kBatch) {
+    BatchHeader* hdr = batch_header(bref);
+    if (tid == 0) sm_item = atomicAdd(&hdr->attn_counter, 1);
+    __syncthreads();                    // every role is done with the previous item; sm_item is set
+    const int item = sm_item;
+    if (item >= hdr->n_attn_items || abort_flag != 0) break;     // CTA-uniform
+    const int2 w = __ldg(reinterpret_cast<const int2*>(bref.table + bref.off_items) + item);
+    h = w.y >> 16;
+    qt = w.y & 0xFFFF;
+    if (w.x != cur_request) {
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(bref.table + bref.off_geoms + static_cast<size_t>(w.x) * sizeof(Geom));
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&sm_geom);
+      if (tid < static_cast<int>(sizeof(Geom) / 4)) dst[tid] = src[tid];
+      cur_request = w.x;
+    }
+  } else {
+    if (iter > 0) break;
+    qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
+    h = blockIdx.y;
+  }
 
+  Ctx ctx{smem + kOffBar, nullptr, &abort_flag};
   if (tid == 0) {
-    abort_flag = 0;
     const uint32_t b = ctx.bars;
+    if (iter > 0) {
+      for (int i = 0; i < B_COUNT; ++i) mbar_inval(b + i * 8);
+    }
     mbar_init(b + B_QFULL * 8, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(b + (B_KFULL + i) * 8, 1);
@@ -236,7 +266,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
     mbar_init_fence();
     fence_async_smem();
   }
-  if (warp == kProducerWarp) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+  if (kBatch) __syncthreads();          // the staged geometry is visible
+  ctx.status = g.status;
+  const int kvh = h / (g.Hq / g.Hkv);
+  const int m0 = qt * kQTile;
+
+  // keys this CTA visits, in local (this call's) positions
+  long long hi_ll = static_cast<long long>(g.prefix) + m0 + kQTile - g.kv_pos0;
+  const int hi = static_cast<int>(hi_ll < 0 ? 0 : (hi_ll > g.N ? g.N : hi_ll));
+  const int ntile = (hi + kTile - 1) / kTile;
+  const int npair = (ntile + 1) / 2;
+
   if (tid < 128) {
     sm_vmean[tid] = g.vmean[kvh * kD + tid];
     sm_vmean[tid + 128] = g.vmean[kvh * kD + tid + 128];
@@ -245,7 +285,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = tmem_slot;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------ producer
@@ -533,6 +572,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
     }
   }
 
+  if (!kBatch) break;
+  }   // work items
+
   __syncthreads();
   if (warp == kProducerWarp) {
     tc_fence_after();
@@ -542,36 +584,61 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(Geom g) {
 
 }  // namespace
 
-int launch_attention(const Geom& g, cudaStream_t s, bool dump) {
+namespace {
+
+// Opt the kernel instantiations into their dynamic shared memory once per device.
+int configure_once() {
   static std::atomic<bool> configured[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { note_cuda_error(e, "cudaGetDevice"); return AKL_ERR_CUDA; }
-  if (dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-    // idempotent, so a race between host threads only repeats the calls
-    const void* kernels[4] = {
-        reinterpret_cast<const void*>(attn_sm100_kernel<false, false>), reinterpret_cast<const void*>(attn_sm100_kernel<false, true>),
-        reinterpret_cast<const void*>(attn_sm100_kernel<true, false>), reinterpret_cast<const void*>(attn_sm100_kernel<true, true>)};
-    for (const void* k : kernels) {
-      e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-      if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(attn)"); return AKL_ERR_CUDA; }
-    }
-    if (dev < 64) configured[dev].store(true, std::memory_order_release);
+  if (dev >= 0 && dev < 64 && configured[dev].load(std::memory_order_acquire)) return AKL_OK;
+  // idempotent, so a race between host threads only repeats the calls
+  const void* kernels[6] = {
+      reinterpret_cast<const void*>(attn_sm100_kernel<false, false, false>), reinterpret_cast<const void*>(attn_sm100_kernel<false, true, false>),
+      reinterpret_cast<const void*>(attn_sm100_kernel<true, false, false>), reinterpret_cast<const void*>(attn_sm100_kernel<true, true, false>),
+      reinterpret_cast<const void*>(attn_sm100_kernel<false, false, true>), reinterpret_cast<const void*>(attn_sm100_kernel<false, true, true>)};
+  for (const void* k : kernels) {
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(attn)"); return AKL_ERR_CUDA; }
   }
+  if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+  return AKL_OK;
+}
+
+}  // namespace
+
+int launch_attention(const Geom& g, cudaStream_t s, bool dump) {
+  int rc = configure_once();
+  if (rc != AKL_OK) return rc;
   dim3 grid(g.mtiles, g.Hq);
   const bool i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
+  const BatchRef none{};
 #ifdef AKL_TRACE
   dump = false;   // development build: the dump pointer receives the timeline, not the scores
 #endif
   if (dump) {
-    if (i8) attn_sm100_kernel<true, true><<<grid, kThreads, kSmemBytes, s>>>(g);
-    else attn_sm100_kernel<true, false><<<grid, kThreads, kSmemBytes, s>>>(g);
+    if (i8) attn_sm100_kernel<true, true, false><<<grid, kThreads, kSmemBytes, s>>>(g, none);
+    else attn_sm100_kernel<true, false, false><<<grid, kThreads, kSmemBytes, s>>>(g, none);
   } else {
-    if (i8) attn_sm100_kernel<false, true><<<grid, kThreads, kSmemBytes, s>>>(g);
-    else attn_sm100_kernel<false, false><<<grid, kThreads, kSmemBytes, s>>>(g);
+    if (i8) attn_sm100_kernel<false, true, false><<<grid, kThreads, kSmemBytes, s>>>(g, none);
+    else attn_sm100_kernel<false, false, false><<<grid, kThreads, kSmemBytes, s>>>(g, none);
   }
-  e = cudaGetLastError();
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { note_cuda_error(e, "attn_sm100_kernel"); return AKL_ERR_CUDA; }
+  return AKL_OK;
+}
+
+// Persistent form over the request table: one CTA per SM.
+int launch_batch_attention(const BatchRef& b, bool qk_i8, int sm_count, cudaStream_t s) {
+  int rc = configure_once();
+  if (rc != AKL_OK) return rc;
+  Geom unused;
+  std::memset(&unused, 0, sizeof(unused));
+  if (qk_i8) attn_sm100_kernel<false, true, true><<<sm_count, kThreads, kSmemBytes, s>>>(unused, b);
+  else attn_sm100_kernel<false, false, true><<<sm_count, kThreads, kSmemBytes, s>>>(unused, b);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { note_cuda_error(e, "attn_sm100_kernel(batch)"); return AKL_ERR_CUDA; }
   return AKL_OK;
 }
 

@@ -58,6 +58,35 @@ struct Geom {
   float sm_scale;
 };
 
+// ---- request table of the batched entry ----------------------------------------------
+// One buffer, written on the host by akl_batch_plan and read by the batch kernels:
+//   BatchHeader | Geom[max_requests] | stat_off[max_requests + 1] | qcta_off[max_requests + 1]
+//   | attention work items (int2 {request, q head << 16 | q tile}), longest first.
+// stat_off / qcta_off are running totals of the statistics items (64-row tile x kv head) and
+// of the Q-quantisation CTAs per request, so a flat item index is mapped back to its request
+// by a binary search.
+struct BatchHeader {
+  int32_t magic;
+  int32_t n_requests;
+  int32_t n_stat_items;
+  int32_t n_q_ctas;
+  int32_t n_attn_items;
+  int32_t attn_counter;   // device side: next attention work item (reset by the means launch)
+  int32_t reserved[10];
+};
+static_assert(sizeof(BatchHeader) == 64, "table header is 64 bytes");
+constexpr int32_t kBatchMagic = 0x424c4b41;
+
+struct BatchRef {
+  uint8_t* table;
+  uint32_t off_geoms, off_stat_off, off_qcta_off, off_items;
+  int32_t max_requests;
+};
+
+__host__ __device__ __forceinline__ BatchHeader* batch_header(const BatchRef& b) {
+  return reinterpret_cast<BatchHeader*>(b.table);
+}
+
 // Byte offset of (row r, byte column c) inside a [rows][128 B] plane stored with the
 // 128-byte swizzle the tensor-core shared-memory descriptors expect: the 16-byte chunk
 // index is XORed with the row index modulo 8.
@@ -162,6 +191,11 @@ int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t
 int launch_quantize_q(const Geom& g, cudaStream_t s);
 int launch_attention(const Geom& g, cudaStream_t s, bool dump = false);
 int launch_merge(const akl_merge_t& m, cudaStream_t s);
+// batched forms: every kernel reads counts and per-request geometry from the request table
+int launch_batch_stats(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s);
+int launch_batch_means(const BatchRef& b, int kv_heads, cudaStream_t s);
+int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s);
+int launch_batch_attention(const BatchRef& b, bool qk_i8, int sm_count, cudaStream_t s);
 void note_cuda_error(cudaError_t e, const char* where);
 
 }  // namespace akl

@@ -26,18 +26,15 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta);
 
 // Flat grid: CTAs [0, nt*Hkv) take one (tile, kv head) each; with kWithQ the CTAs after them
 // quantise Q rows, so that the two independent passes share one launch and overlap.
-template <int KV_DTYPE, int IDX_DTYPE, bool kWithQ>
-__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_kernel(Geom g) {
+// `item` = tile * Hkv + kv head.  Ends with every thread past its last shared-memory read of
+// the tile, but not synchronised: a caller that runs several items per CTA synchronises between them.
+template <int KV_DTYPE, int IDX_DTYPE>
+__device__ __forceinline__ void kv_tile_stats_item(const Geom& g, int item) {
   __shared__ float sm_k[8][kD];
   __shared__ float sm_v[8][kD];
   __shared__ float sm_mx[8][kD];
   __shared__ float sm_mn[8][kD];
-  const int nstat = g.nt * g.Hkv;
-  if (kWithQ && static_cast<int>(blockIdx.x) >= nstat) {
-    quantize_q_rows(g, static_cast<long long>(blockIdx.x) - nstat);
-    return;
-  }
-  const int t = blockIdx.x / g.Hkv, kvh = blockIdx.x % g.Hkv;
+  const int t = item / g.Hkv, kvh = item % g.Hkv;
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
 
@@ -104,6 +101,16 @@ __global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_kernel(Geom g) {
   g.vtmin[(static_cast<size_t>(kvh) * g.ntiles_cap + t) * kD + c] = vmn;
 }
 
+template <int KV_DTYPE, int IDX_DTYPE, bool kWithQ>
+__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_kernel(Geom g) {
+  const int nstat = g.nt * g.Hkv;
+  if (kWithQ && static_cast<int>(blockIdx.x) >= nstat) {
+    quantize_q_rows(g, static_cast<long long>(blockIdx.x) - nstat);
+    return;
+  }
+  kv_tile_stats_item<KV_DTYPE, IDX_DTYPE>(g, blockIdx.x);
+}
+
 // ---------------------------------------------------------------------------
 // 2. channel means (ordered: tiles inside a 32768-row slab, then slabs) and the
 //    centred per-tile V amax  (quant.py:566-581)
@@ -126,11 +133,11 @@ __device__ __forceinline__ void write_tile_scales(const Geom& g, int kvh, int t,
 // centred per-tile V amax.  With `fuse_scales` (one GPU holds the whole request) the per-tile V
 // scales and fold arrays follow in the same launch.
 template <bool kFuseScales>
-__global__ void __launch_bounds__(kMeansThreads) kv_means_kernel(Geom g) {
+__device__ __forceinline__ void kv_means_head(const Geom& g, int kvh) {
   __shared__ float sm_vmean[kD];
   __shared__ float sm_wmax[32];
   __shared__ float sm_vsm;
-  const int kvh = blockIdx.x, tid = threadIdx.x;
+  const int tid = threadIdx.x;
   const int ntg = g.ntiles_global;
   if (tid < 2 * kD) {
     const int c = tid & (kD - 1);
@@ -196,6 +203,11 @@ __global__ void __launch_bounds__(kMeansThreads) kv_means_kernel(Geom g) {
   }
 }
 
+template <bool kFuseScales>
+__global__ void __launch_bounds__(kMeansThreads) kv_means_kernel(Geom g) {
+  kv_means_head<kFuseScales>(g, blockIdx.x);
+}
+
 // ---------------------------------------------------------------------------
 // 3. per-tile V scales and the fold arrays  (quant.py:576-584, :673-679)
 // ---------------------------------------------------------------------------
@@ -213,12 +225,10 @@ __global__ void __launch_bounds__(kThreads) kv_scales_kernel(Geom g) {
 //    (quant.py:589-668).  blockIdx.z: 0 = K, 1 = V.
 // ---------------------------------------------------------------------------
 template <int KV_DTYPE, int IDX_DTYPE>
-__global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
+__device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh, bool is_v) {
   constexpr int kVRow = 80;                       // padded 64-byte row, keeps 16 B alignment
   __shared__ float sm_red[8];
   __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
-  const int t = blockIdx.x, kvh = blockIdx.y;
-  const bool is_v = blockIdx.z == 1;
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
   const void* pool = is_v ? g.v_pool : g.k_pool;
@@ -322,6 +332,11 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
   }
 }
 
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
+  kv_transform_item<KV_DTYPE, IDX_DTYPE>(g, blockIdx.x, blockIdx.y, blockIdx.z == 1);
+}
+
 // ---------------------------------------------------------------------------
 // 5. Q: rotate, per-row amax, E4M3, scale*sm_scale  (quant.py:433-480)
 //    one warp per (head, padded row); rows >= T are zero bytes with the clamp scale
@@ -384,6 +399,97 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
 }
 
 __global__ void __launch_bounds__(kThreads) quantize_q_kernel(Geom g) { quantize_q_rows(g, blockIdx.x); }
+
+// ---------------------------------------------------------------------------
+// Batched forms: the same per-item bodies, driven by the request table.  Grids are sized
+// from the capacities only; each CTA walks the flat item range with a grid stride, finds an
+// item's request by binary search in the running totals, and keeps that request's geometry
+// in shared memory until the request changes.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int find_request(const int* totals, int n, int item) {
+  // largest r in [0, n) with totals[r] <= item   (totals[0] = 0, totals[n] > item)
+  int lo = 0, hi = n;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(totals + mid) <= item) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// All threads of the CTA; `cur` is the request whose geometry `sg` holds (-1: none).
+__device__ __forceinline__ void stage_geom(const BatchRef& b, int r, int& cur, Geom* sg) {
+  if (r == cur) return;                              // CTA-uniform
+  __syncthreads();                                   // nobody still reads the old geometry
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(b.table + b.off_geoms + static_cast<size_t>(r) * sizeof(Geom));
+  uint32_t* dst = reinterpret_cast<uint32_t*>(sg);
+  for (int i = threadIdx.x; i < static_cast<int>(sizeof(Geom) / 4); i += blockDim.x) dst[i] = src[i];
+  __syncthreads();
+  cur = r;
+}
+
+// The per-item bodies are called, not inlined, in the batch kernels: the loop state then lives
+// across a call boundary instead of competing with the body for registers.
+template <int KV_DTYPE, int IDX_DTYPE>
+__device__ __noinline__ void stats_or_q_item(const Geom& g, int in_req, bool is_q) {
+  if (is_q) quantize_q_rows(g, in_req);
+  else kv_tile_stats_item<KV_DTYPE, IDX_DTYPE>(g, in_req);
+}
+
+template <int KV_DTYPE, int IDX_DTYPE>
+__device__ __noinline__ void transform_item_call(const Geom& g, int in_req, bool is_v) {
+  kv_transform_item<KV_DTYPE, IDX_DTYPE>(g, in_req / g.Hkv, in_req % g.Hkv, is_v);
+}
+
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_batch_kernel(BatchRef b) {
+  __shared__ Geom sg;
+  const BatchHeader* hdr = batch_header(b);
+  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = n_stat + hdr->n_q_ctas;
+  const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
+  const int* qcta_off = reinterpret_cast<const int*>(b.table + b.off_qcta_off);
+  int cur = -1;
+  for (int item = blockIdx.x; item < n_all; item += gridDim.x) {
+    const bool is_q = item >= n_stat;
+    const int local = is_q ? item - n_stat : item;
+    const int* totals = is_q ? qcta_off : stat_off;
+    const int r = find_request(totals, n_req, local);
+    stage_geom(b, r, cur, &sg);
+    const int in_req = local - __ldg(totals + r);
+    stats_or_q_item<KV_DTYPE, IDX_DTYPE>(sg, in_req, is_q);
+    __syncthreads();                                 // the item's shared-memory partials are dead
+  }
+}
+
+// One CTA per (request, kv head) up to the request capacity; CTA 0 also rewinds the attention
+// work counter for the attention launch that follows in stream order.
+__global__ void __launch_bounds__(kMeansThreads) kv_means_batch_kernel(BatchRef b, int kv_heads) {
+  __shared__ Geom sg;
+  BatchHeader* hdr = batch_header(b);
+  if (blockIdx.x == 0 && threadIdx.x == 0) hdr->attn_counter = 0;
+  const int r = blockIdx.x / kv_heads, kvh = blockIdx.x % kv_heads;
+  if (r >= hdr->n_requests) return;
+  int cur = -1;
+  stage_geom(b, r, cur, &sg);
+  kv_means_head<true>(sg, kvh);
+}
+
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRef b) {
+  __shared__ Geom sg;
+  const BatchHeader* hdr = batch_header(b);
+  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items;
+  const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
+  int cur = -1;
+  for (int item = blockIdx.x; item < 2 * n_stat; item += gridDim.x) {
+    const bool is_v = item >= n_stat;
+    const int local = is_v ? item - n_stat : item;
+    const int r = find_request(stat_off, n_req, local);
+    stage_geom(b, r, cur, &sg);
+    const int in_req = local - __ldg(stat_off + r);
+    transform_item_call<KV_DTYPE, IDX_DTYPE>(sg, in_req, is_v);
+    __syncthreads();
+  }
+}
 
 }  // namespace
 
@@ -449,6 +555,40 @@ int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t
   else
     kv_transform_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(g);
   AKL_LAUNCH_CHECK("kv_transform");
+  return AKL_OK;
+}
+
+int launch_batch_stats(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>(sm_count) * 4u;        // four resident CTAs per SM
+  if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
+    kv_tile_stats_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+  else if (kv_dtype == AKL_KV_BF16)
+    kv_tile_stats_batch_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+  else if (idx_dtype == AKL_IDX_I64)
+    kv_tile_stats_batch_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+  else
+    kv_tile_stats_batch_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+  AKL_LAUNCH_CHECK("kv_tile_stats_batch");
+  return AKL_OK;
+}
+
+int launch_batch_means(const BatchRef& b, int kv_heads, cudaStream_t s) {
+  kv_means_batch_kernel<<<static_cast<unsigned>(b.max_requests) * kv_heads, kMeansThreads, 0, s>>>(b, kv_heads);
+  AKL_LAUNCH_CHECK("kv_means_batch");
+  return AKL_OK;
+}
+
+int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
+  const unsigned grid = static_cast<unsigned>(sm_count) * 3u;        // three resident CTAs per SM
+  if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
+    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+  else if (kv_dtype == AKL_KV_BF16)
+    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+  else if (idx_dtype == AKL_IDX_I64)
+    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+  else
+    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+  AKL_LAUNCH_CHECK("kv_transform_batch");
   return AKL_OK;
 }
 

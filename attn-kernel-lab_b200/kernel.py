@@ -36,6 +36,7 @@ EXPORTS = (
     "akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales",
     "akl_kv_transform", "akl_quantize_q", "akl_attention", "akl_attention_dump",
     "akl_merge_states", "akl_prefill_extend_static_scratch",
+    "akl_batch_layout", "akl_batch_plan", "akl_prefill_extend_batch",
 )
 
 AKL_OK = 0
@@ -80,6 +81,34 @@ class Merge(ctypes.Structure):
     _fields_ = [("parts_o", ctypes.c_void_p), ("parts_lse", ctypes.c_void_p),
                 ("out", ctypes.c_void_p), ("lse_out", ctypes.c_void_p),
                 ("nparts", ctypes.c_int32), ("rows", ctypes.c_int32)]
+
+
+class BatchCaps(ctypes.Structure):
+    _fields_ = [("max_requests", ctypes.c_int32), ("max_total_kv_pairs", ctypes.c_int32),
+                ("max_total_q_tiles", ctypes.c_int32), ("q_heads", ctypes.c_int32),
+                ("kv_heads", ctypes.c_int32), ("reserved_", ctypes.c_int32)]
+
+
+class BatchLayout(ctypes.Structure):
+    _fields_ = [("workspace_bytes", ctypes.c_uint64), ("table_bytes", ctypes.c_uint64),
+                ("ws_off_status", ctypes.c_uint64),
+                ("table_off_geoms", ctypes.c_uint32), ("table_geom_stride", ctypes.c_uint32),
+                ("table_off_stat_totals", ctypes.c_uint32), ("table_off_qcta_totals", ctypes.c_uint32),
+                ("table_off_items", ctypes.c_uint32), ("reserved_", ctypes.c_uint32)]
+
+
+class BatchRequest(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k_pool", ctypes.c_void_p), ("v_pool", ctypes.c_void_p),
+                ("idx", ctypes.c_void_p), ("out", ctypes.c_void_p), ("lse_out", ctypes.c_void_p),
+                ("T", ctypes.c_int32), ("N", ctypes.c_int32), ("prefix", ctypes.c_int32),
+                ("reserved_", ctypes.c_int32)]
+
+
+class Batch(ctypes.Structure):
+    _fields_ = [("caps", BatchCaps), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_uint64),
+                ("table", ctypes.c_void_p), ("table_bytes", ctypes.c_uint64),
+                ("kv_dtype", ctypes.c_int32), ("idx_dtype", ctypes.c_int32),
+                ("flags", ctypes.c_uint32), ("sm_scale", ctypes.c_float)]
 
 
 class NativeError(RuntimeError):
@@ -178,6 +207,13 @@ def load():
         lib.akl_attention_dump.restype = ctypes.c_int
         lib.akl_merge_states.argtypes = [ctypes.POINTER(Merge), ctypes.c_void_p]
         lib.akl_merge_states.restype = ctypes.c_int
+        lib.akl_batch_layout.argtypes = [ctypes.POINTER(BatchCaps), ctypes.POINTER(BatchLayout)]
+        lib.akl_batch_layout.restype = ctypes.c_int
+        lib.akl_batch_plan.argtypes = [ctypes.POINTER(Batch), ctypes.POINTER(BatchRequest), ctypes.c_int32,
+                                       ctypes.c_void_p]
+        lib.akl_batch_plan.restype = ctypes.c_int
+        lib.akl_prefill_extend_batch.argtypes = [ctypes.POINTER(Batch), ctypes.c_void_p]
+        lib.akl_prefill_extend_batch.restype = ctypes.c_int
         _lib = lib
     return _lib
 

@@ -30,8 +30,8 @@ _PAGE_SIZE = 1
 _MODE = "extend"
 _MASK = "bottom_right_causal"
 
-__all__ = ["PrefillRequest", "check_request", "plan_workspace", "prefill_extend",
-           "prefill_extend_batch"]
+__all__ = ["PrefillRequest", "check_request", "plan_workspace", "plan_batch_workspace",
+           "prefill_extend", "prefill_extend_batch"]
 
 
 @dataclass(frozen=True)
@@ -297,6 +297,68 @@ def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, 
     return (out, lse) if request.return_lse else out
 
 
+def plan_batch_workspace(device, *, max_requests: int, max_total_kv_len: int, max_total_q_len: int,
+                         q_heads: int | None = None, kv_heads: int | None = None,
+                         capability: OperatorCapability = V1_CAPABILITY):
+    """Capacity-reserved scratch for `prefill_extend_batch`'s native path, sized from totals over a
+    batch (sum of kv lengths, sum of extend lengths).  Head counts are validated against the
+    declared surface like `plan_workspace` does."""
+    from .quant import FP8PrefillBatchWorkspace
+
+    q_heads = max(capability.q_heads) if q_heads is None else int(q_heads)
+    kv_heads = max(capability.kv_heads) if kv_heads is None else int(kv_heads)
+    check_supported(head_dim=max(capability.head_dim), q_heads=q_heads, kv_heads=kv_heads,
+                    page_size=_PAGE_SIZE, mode=_MODE, mask=_MASK, kv_dtype=capability.kv_dtypes[0],
+                    return_lse=False, capability=capability)
+    return FP8PrefillBatchWorkspace(device, max_requests=max_requests, max_total_kv_len=max_total_kv_len,
+                                    max_total_q_len=max_total_q_len, q_heads=q_heads, kv_heads=kv_heads)
+
+
+def _native_batch(requests, ws, *, sm_scale, qk_i8, rotate, center_k, return_lse, capability):
+    """Validate every request, give the ones without `out` / `lse_out` their tensors, group by
+    (kv dtype, idx dtype) -- one native batch per group, normally one -- and launch."""
+    import torch
+
+    from .quant import WorkspaceCapacityError
+
+    if not isinstance(qk_i8, bool):
+        raise TypeError(f"qk_i8 must be a bool, got {type(qk_i8).__name__}")
+    checked = []
+    for r in requests:
+        checked.append(check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"], workspace=None,
+                                     out=r.get("out"), lse_out=r.get("lse_out"), sm_scale=sm_scale,
+                                     return_lse=return_lse, capability=capability))
+    if not requests:
+        return []
+    device = requests[0]["q"].device
+    if device.type != "cuda":
+        raise RuntimeError(
+            f"prefill_extend_batch needs CUDA tensors, got q on {device}: this operator has no CPU path")
+    ws_device = torch.device(ws.device)
+    for r, c in zip(requests, checked):
+        if not _same_device(r["q"].device, ws_device):
+            _reject(f"workspace is on {ws_device} but q is on {r['q'].device}", field="workspace",
+                    value=str(ws_device), supported=str(r["q"].device))
+        if (c.q_heads, c.kv_heads) != (ws.q_heads, ws.kv_heads):
+            raise WorkspaceCapacityError(
+                f"request heads {c.q_heads}:{c.kv_heads} differ from the batch workspace's "
+                f"{ws.q_heads}:{ws.kv_heads}; the allocation never changes shape")
+    filled, groups = [], {}
+    for i, (r, c) in enumerate(zip(requests, checked)):
+        d = dict(r)
+        if d.get("out") is None:
+            d["out"] = torch.empty_like(r["q"])
+        if c.return_lse and d.get("lse_out") is None:
+            d["lse_out"] = torch.empty((c.q_len, c.q_heads), dtype=torch.float32, device=device)
+        filled.append(d)
+        groups.setdefault((r["k_pool"].dtype, r["idx"].dtype), []).append(i)
+    for members in groups.values():
+        plan = ws.plan([filled[i] for i in members], sm_scale=checked[members[0]].sm_scale,
+                       rotate=rotate, center_k=center_k, qk_i8=qk_i8)
+        ws.launch(plan)
+    return [(d["out"], d["lse_out"]) if c.return_lse else d["out"] for d, c in zip(filled, checked)]
+
+
 _side_streams: dict = {}
 
 
@@ -321,7 +383,10 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Tr
     `requests`: iterable of dicts with keys q, k_pool, v_pool, idx, prefix and optionally out,
     lse_out.  Every request is validated before the first launch.
 
-    `workspace`: one workspace -> the requests run back to back on the current stream.
+    `workspace`: an `FP8PrefillBatchWorkspace` (from `plan_batch_workspace`) -> the native batched
+    entry: four launches for the whole batch, per-request lengths and pointers in a device table,
+    one persistent attention launch that draws (request, head, query tile) items longest first.
+    One `FP8PrefillWorkspace` -> the requests run back to back on the current stream.
     A list/tuple of K workspaces -> K side streams, one workspace each; the requests are dealt to
     them longest first onto the least loaded stream (cost = attended pairs), so that the streams
     finish together.  Requests are independent units, so the gather/quantise kernels of one
@@ -330,6 +395,11 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Tr
     whole batch can be captured in one CUDA graph); callers see ordinary stream semantics.
     Returns the list of results in request order."""
     requests = list(requests)
+    from .quant import FP8PrefillBatchWorkspace
+
+    if isinstance(workspace, FP8PrefillBatchWorkspace):
+        return _native_batch(requests, workspace, sm_scale=sm_scale, qk_i8=qk_i8, rotate=rotate,
+                             center_k=center_k, return_lse=return_lse, capability=capability)
     pool = list(workspace) if isinstance(workspace, (list, tuple)) else [workspace]
     for i, r in enumerate(requests):
         check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"],

@@ -229,6 +229,138 @@ class FP8PrefillWorkspace:
         return dk.permute(0, 1, 3, 2).reshape(img.shape[0], npairs * 128, HEAD_DIM)[:, :npad]
 
 
+class BatchPlan:
+    """A request table as `akl_batch_plan` wrote it, in pinned host memory, plus what is needed to
+    launch it.  `FP8PrefillBatchWorkspace.launch(plan)` copies it to the device and enqueues the
+    four kernels; a captured CUDA graph that holds that copy re-reads this host buffer at every
+    replay, so `FP8PrefillBatchWorkspace.replan(plan, requests)` followed by a replay runs the new
+    lengths and tensors without re-capturing."""
+
+    def __init__(self, table_host, batch, n_requests):
+        self.table_host = table_host
+        self.batch = batch
+        self.n_requests = n_requests
+
+
+class FP8PrefillBatchWorkspace:
+    """Capacity-reserved scratch for the batched entry `akl_prefill_extend_batch`: ONE device
+    allocation shared by all requests of a batch (each request's tiles are packed behind the
+    previous request's) and one device copy of the request table.  Sized once from totals; never
+    reallocates.  A batch that needs more raises `WorkspaceCapacityError`.
+
+    The capacities are totals over a batch: `max_total_kv_len` >= sum of kv lengths and
+    `max_total_q_len` >= sum of extend lengths (each request rounds up to whole 128-row tiles;
+    room for that rounding is added per request)."""
+
+    def __init__(self, device, *, max_requests: int, max_total_kv_len: int, max_total_q_len: int,
+                 q_heads: int = DECLARED_Q_HEADS, kv_heads: int = DECLARED_KV_HEADS):
+        for name, value in (("max_requests", max_requests), ("max_total_kv_len", max_total_kv_len),
+                            ("max_total_q_len", max_total_q_len), ("q_heads", q_heads), ("kv_heads", kv_heads)):
+            if isinstance(value, bool) or not isinstance(value, int) or value < 1:
+                raise ValueError(f"{name} must be an int >= 1, got {value!r}")
+        if q_heads % kv_heads:
+            raise ValueError(f"q_heads={q_heads} must be divisible by kv_heads={kv_heads}")
+        self.device = torch.device(device)
+        self.caps = _kernel.BatchCaps(
+            max_requests, _ceil_to(max_total_kv_len, 128) // 128 + max_requests,
+            _ceil_to(max_total_q_len, MPAD) // MPAD + max_requests, q_heads, kv_heads, 0)
+        lay = _kernel.BatchLayout()
+        _kernel.check(_kernel.load().akl_batch_layout(ctypes.byref(self.caps), ctypes.byref(lay)),
+                      "akl_batch_layout")
+        self._ws_bytes, self._table_bytes = int(lay.workspace_bytes), int(lay.table_bytes)
+        buf = torch.empty(self._ws_bytes + 1024, dtype=torch.uint8, device=self.device)
+        shift = (-buf.data_ptr()) % 1024
+        self._buf = buf
+        self._base = buf[shift:shift + self._ws_bytes]
+        self._table_dev = torch.empty(self._table_bytes + 16, dtype=torch.uint8, device=self.device)
+        tshift = (-self._table_dev.data_ptr()) % 16
+        self._table = self._table_dev[tshift:tshift + self._table_bytes]
+        self.layout = lay
+        self._status = self._base[int(lay.ws_off_status):int(lay.ws_off_status) + 256].view(torch.int32)
+        self._status.zero_()
+        self._held = []          # host tables a captured graph still reads
+
+    @property
+    def q_heads(self) -> int:
+        return int(self.caps.q_heads)
+
+    @property
+    def kv_heads(self) -> int:
+        return int(self.caps.kv_heads)
+
+    def nbytes(self) -> int:
+        return self._ws_bytes + self._table_bytes
+
+    def base_ptr(self) -> int:
+        return self._base.data_ptr()
+
+    def status(self) -> int:
+        """First device-side error code recorded since allocation (synchronises)."""
+        return int(self._status[0].item())
+
+    # ------------------------------------------------------------------ planning
+    def _batch_struct(self, kv_dtype, idx_dtype, flags, sm_scale):
+        b = _kernel.Batch()
+        b.caps = self.caps
+        b.workspace, b.workspace_bytes = self._base.data_ptr(), self._ws_bytes
+        b.table, b.table_bytes = self._table.data_ptr(), self._table_bytes
+        b.kv_dtype, b.idx_dtype, b.flags, b.sm_scale = kv_dtype, idx_dtype, flags, float(sm_scale)
+        return b
+
+    @staticmethod
+    def _request_array(requests):
+        arr = (_kernel.BatchRequest * max(1, len(requests)))()
+        for i, r in enumerate(requests):
+            a = arr[i]
+            a.q, a.k_pool, a.v_pool = r["q"].data_ptr(), r["k_pool"].data_ptr(), r["v_pool"].data_ptr()
+            a.idx, a.out = r["idx"].data_ptr(), r["out"].data_ptr()
+            lse = r.get("lse_out")
+            a.lse_out = lse.data_ptr() if lse is not None else None
+            a.T, a.N, a.prefix = int(r["q"].shape[0]), int(r["idx"].shape[0]), int(r["prefix"])
+        return arr
+
+    def _fill(self, table_host, batch, requests):
+        arr = self._request_array(requests)
+        code = _kernel.load().akl_batch_plan(ctypes.byref(batch), arr, len(requests), table_host.data_ptr())
+        if code == _kernel.AKL_ERR_CAPACITY:
+            raise WorkspaceCapacityError(
+                f"batch of {len(requests)} requests (sum kv {sum(int(r['idx'].shape[0]) for r in requests)}, "
+                f"sum q {sum(int(r['q'].shape[0]) for r in requests)}) is outside the batch capacities "
+                f"(requests {self.caps.max_requests}, kv pairs {self.caps.max_total_kv_pairs}, "
+                f"q tiles {self.caps.max_total_q_tiles}); the allocation never grows")
+        _kernel.check(code, "akl_batch_plan")
+
+    def plan(self, requests, *, sm_scale: float, rotate: bool = True, center_k: bool = True,
+             qk_i8: bool = False) -> BatchPlan:
+        """Host-side only: pack `requests` (dicts with q, k_pool, v_pool, idx, prefix, out and
+        optionally lse_out; one kv dtype and one idx dtype) into a fresh pinned request table."""
+        requests = list(requests)
+        if not requests:
+            raise ValueError("an empty batch has nothing to plan")
+        flags = ((_kernel.AKL_FLAG_ROTATE if rotate else 0) | (_kernel.AKL_FLAG_CENTER_K if center_k else 0)
+                 | (_kernel.AKL_FLAG_QK_I8 if qk_i8 else 0))
+        batch = self._batch_struct(_dtype_code(requests[0]["k_pool"]), _idx_code(requests[0]["idx"]), flags, sm_scale)
+        pin = self.device.type == "cuda"
+        table_host = torch.empty(self._table_bytes, dtype=torch.uint8, pin_memory=pin)
+        self._fill(table_host, batch, requests)
+        return BatchPlan(table_host, batch, len(requests))
+
+    def replan(self, plan: BatchPlan, requests) -> None:
+        """Rewrite `plan`'s host table in place for other requests (same dtypes and modes)."""
+        requests = list(requests)
+        self._fill(plan.table_host, plan.batch, requests)
+        plan.n_requests = len(requests)
+
+    def launch(self, plan: BatchPlan) -> None:
+        """Copy the table to the device and enqueue the four kernels on the current stream."""
+        self._table.copy_(plan.table_host, non_blocking=True)
+        if torch.cuda.is_current_stream_capturing():
+            self._held.append(plan)      # the graph's copy node reads this host buffer at replay
+        with torch.cuda.device(self.device):
+            code = _kernel.load().akl_prefill_extend_batch(ctypes.byref(plan.batch), _stream(self.device))
+        _kernel.check(code, "akl_prefill_extend_batch")
+
+
 def _unswizzle_planes(img: torch.Tensor) -> torch.Tensor:
     """[..., 2, 128 rows, 128 B swizzled] -> [..., 128 rows, 256 B]."""
     rows = torch.arange(128, device=img.device)[:, None]

@@ -168,6 +168,83 @@ int akl_attention_dump(const akl_call_t* call, float* s_dump, uint8_t* p_dump, v
 
 int akl_merge_states(const akl_merge_t* m, void* stream);
 
+/* ---- batched variable-length entry --------------------------------------------------
+ * R independent requests in FOUR launches (statistics + Q quantisation, means + scales,
+ * K/V transform, attention) instead of four per request.  Replaces the per-request Python
+ * loop of the reference's engine backend
+ * (engines/sglang/integration/fp8_prefill/backend.py:267-289); every request's result is
+ * bit-equal to akl_prefill_extend on the same inputs.
+ *
+ * Lengths, pointers and offsets of the requests live in a REQUEST TABLE in device memory,
+ * which the kernels read; the launch itself depends only on the capacities.  So a CUDA graph
+ * that holds akl_prefill_extend_batch can be replayed after the table's contents changed
+ * (other lengths, other request count, other tensors), as long as they fit the capacities.
+ * The host fills a host copy of the table with akl_batch_plan and copies it to the device
+ * (the copy may itself be a node of the graph).  The attention launch is persistent: one
+ * CTA per SM draws (request, q head, 128-row tile) work items, longest first, from a list in
+ * the table through an atomic counter. */
+typedef struct akl_batch_caps {
+  int32_t max_requests;
+  int32_t max_total_kv_pairs;  /* capacity in 128-key tile pairs: >= sum_r ceil(N_r / 128) */
+  int32_t max_total_q_tiles;   /* capacity in 128-row query tiles: >= sum_r ceil(T_r / 128) */
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t reserved_;
+} akl_batch_caps_t;
+
+typedef struct akl_batch_layout {
+  uint64_t workspace_bytes;    /* device scratch shared by the batch (1024-byte aligned base) */
+  uint64_t table_bytes;        /* size of the request table, host copy and device copy alike */
+  uint64_t ws_off_status;      /* [64] i32 inside the workspace; word 0 = first device error code */
+  /* inside the table: a 64-byte header of i32 words {magic, n_requests, n_stat_items, n_q_ctas,
+   * n_attn_items, next work item, ...}; one geometry record per request; running totals of the
+   * statistics items and of the Q-quantisation CTAs per request; the attention work list of
+   * {request, q_head << 16 | q_tile} i32 pairs in execution order */
+  uint32_t table_off_geoms;
+  uint32_t table_geom_stride;
+  uint32_t table_off_stat_totals;
+  uint32_t table_off_qcta_totals;
+  uint32_t table_off_items;
+  uint32_t reserved_;
+} akl_batch_layout_t;
+
+typedef struct akl_batch_request {
+  const void* q;        /* [T][Hq][256] bf16 */
+  const void* k_pool;   /* [pool_rows][Hkv][256]; may differ between requests */
+  const void* v_pool;
+  const void* idx;      /* [N] */
+  void* out;            /* [T][Hq][256] bf16 */
+  float* lse_out;       /* [T][Hq] or NULL */
+  int32_t T, N, prefix;
+  int32_t reserved_;
+} akl_batch_request_t;
+
+typedef struct akl_batch {
+  akl_batch_caps_t caps;
+  void* workspace;             /* device, akl_batch_layout_t.workspace_bytes */
+  uint64_t workspace_bytes;
+  void* table;                 /* device copy of the request table (16-byte aligned) */
+  uint64_t table_bytes;
+  int32_t kv_dtype;            /* AKL_KV_*, one for the whole batch */
+  int32_t idx_dtype;           /* AKL_IDX_* */
+  uint32_t flags;              /* AKL_FLAG_* */
+  float sm_scale;
+} akl_batch_t;
+
+/* Sizes for the given capacities.  Pure host arithmetic. */
+int akl_batch_layout(const akl_batch_caps_t* caps, akl_batch_layout_t* out);
+
+/* Validates the requests like akl_prefill_extend validates one, packs them into the batch
+ * workspace, sorts the attention work items longest first and writes the request table into
+ * `table_host` (b->table_bytes bytes of host memory; b->table is not touched).  Pure host
+ * arithmetic: no CUDA call.  AKL_ERR_CAPACITY when the requests exceed b->caps. */
+int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* requests, int32_t n_requests,
+                   void* table_host);
+
+/* The four launches.  b->table must hold (in stream order) a table written by akl_batch_plan
+ * for the same caps, workspace, dtypes and flags. */
+int akl_prefill_extend_batch(const akl_batch_t* b, void* stream);
+
 /* The whole operator (same work and same results as akl_prefill_extend) for callers that cannot
  * allocate device memory -- an engine plugin that is handed no allocator, or a host whose memory
  * pool is frozen after start-up.  The workspace is a 16 MiB array built into the library (held by
