@@ -443,19 +443,25 @@ int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* reqs, int32_
 }
 
 int akl_prefill_extend_batch(const akl_batch_t* b, void* stream) {
+  return akl_prefill_extend_batch_phases(b, AKL_BATCH_ALL, stream);
+}
+
+int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void* stream) {
   BatchLayout L;
   int rc = check_batch(b, &L);
   if (rc != AKL_OK) return rc;
   if (b->table == nullptr) return AKL_ERR_INVALID;
   if (reinterpret_cast<uintptr_t>(b->table) & 15u) return AKL_ERR_ALIGN;
+  if (phases == 0 || (phases & ~AKL_BATCH_ALL)) return AKL_ERR_INVALID;
   int sms = 0;
   if ((rc = device_sm_count(&sms)) != AKL_OK) return rc;
   const BatchRef ref = make_ref(b, L, b->table);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if ((rc = launch_batch_stats(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
-  if ((rc = launch_batch_means(ref, b->caps.kv_heads, s)) != AKL_OK) return rc;
-  if ((rc = launch_batch_transform(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
-  return launch_batch_attention(ref, (b->flags & AKL_FLAG_QK_I8) != 0, sms, s);
+  if ((phases & AKL_BATCH_STATS) && (rc = launch_batch_stats(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
+  if ((phases & AKL_BATCH_MEANS) && (rc = launch_batch_means(ref, b->caps.kv_heads, s)) != AKL_OK) return rc;
+  if ((phases & AKL_BATCH_TRANSFORM) && (rc = launch_batch_transform(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
+  if (phases & AKL_BATCH_ATTENTION) return launch_batch_attention(ref, (b->flags & AKL_FLAG_QK_I8) != 0, sms, s);
+  return AKL_OK;
 }
 
 int akl_merge_states(const akl_merge_t* m, void* stream) {

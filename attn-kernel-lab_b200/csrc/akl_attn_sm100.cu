@@ -450,28 +450,47 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       const float sc = qs * t_ks;
       const int rem = limit - j * kTile;
       float s[64];
-      float rmax[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) rmax[i] = -INFINITY;
+      float rowmax;
+      float sc_late;      // factor still to be applied to s[] before the exponent
       if (rem >= kTile - 1) {
+        // every key of the tile is visible: the row maximum of the scaled scores is the scaled
+        // maximum of the raw ones (sc > 0 and rounding is monotonic, so the bits agree), and
+        // the scaling itself moves into the exponent loop
+        float rmax[8];
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          s[i] = acc_value<kI8>(sr[i]);
-          s[i + 1] = acc_value<kI8>(sr[i + 1]);
-          mul2(s[i], s[i + 1], sc);
-          rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
-          rmax[(i + 1) & 7] = fmaxf(rmax[(i + 1) & 7], s[i + 1]);
+        for (int i = 0; i < 8; ++i) rmax[i] = acc_value<kI8>(sr[i]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = rmax[i];
+#pragma unroll
+        for (int i = 8; i < 64; i += 16) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            s[i + k] = acc_value<kI8>(sr[i + k]);
+            s[i + 8 + k] = acc_value<kI8>(sr[i + 8 + k]);
+            rmax[k] = fmax3(rmax[k], s[i + k], s[i + 8 + k]);
+          }
         }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s[56 + k] = acc_value<kI8>(sr[56 + k]);
+        rowmax = fmax3(fmax3(rmax[0], rmax[1], rmax[2]), fmax3(rmax[3], rmax[4], rmax[5]),
+                       fmax3(rmax[6], rmax[7], fmax3(s[56], s[57], s[58])));
+        rowmax = fmax3(rowmax, fmax3(s[59], s[60], s[61]), fmaxf(s[62], s[63]));
+        rowmax *= sc;
+        sc_late = sc;
       } else {
+        float rmax[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) rmax[i] = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float v = acc_value<kI8>(sr[i]) * sc;
           s[i] = (i <= rem) ? v : -INFINITY;
           rmax[i & 7] = fmaxf(rmax[i & 7], s[i]);
         }
+        rowmax = fmaxf(fmaxf(fmaxf(rmax[0], rmax[1]), fmaxf(rmax[2], rmax[3])),
+                       fmaxf(fmaxf(rmax[4], rmax[5]), fmaxf(rmax[6], rmax[7])));
+        sc_late = 1.0f;     // already scaled; multiplying by one changes nothing (-inf stays -inf)
       }
-      const float rowmax = fmaxf(fmaxf(fmaxf(rmax[0], rmax[1]), fmaxf(rmax[2], rmax[3])),
-                                 fmaxf(fmaxf(rmax[4], rmax[5]), fmaxf(rmax[6], rmax[7])));
       AKL_TRACE_POINT(1);
       // running maximum: take the value after tile j-1 from the other group, publish ours
       float m_prev;
@@ -487,14 +506,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
       m_own = m_new;
       float part[4] = {0.f, 0.f, 0.f, 0.f};
+      // AKL_POLY_GROUPS of the 16 four-element groups send their second pair through the
+      // polynomial on the FMA pipe instead of the MUFU (the two pipes run side by side)
+#ifndef AKL_POLY_GROUPS
+#define AKL_POLY_GROUPS 0
+#endif
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
+        mul2(s[i], s[i + 1], sc_late);
+        mul2(s[i + 2], s[i + 3], sc_late);
         fma2(s[i], s[i + 1], kLog2e, pc);
         fma2(s[i + 2], s[i + 3], kLog2e, pc);
         s[i] = ex2(s[i]);
         s[i + 1] = ex2(s[i + 1]);
-        s[i + 2] = ex2(s[i + 2]);
-        s[i + 3] = ex2(s[i + 3]);
+        if (AKL_POLY_GROUPS > 0 && ((i >> 2) * AKL_POLY_GROUPS) % 16 < AKL_POLY_GROUPS) {
+          s[i + 2] = fmaxf(s[i + 2], -125.f);
+          s[i + 3] = fmaxf(s[i + 3], -125.f);
+          exp2_poly2(s[i + 2], s[i + 3]);
+        } else {
+          s[i + 2] = ex2(s[i + 2]);
+          s[i + 3] = ex2(s[i + 3]);
+        }
         add2(part[0], part[1], s[i], s[i + 1]);
         add2(part[2], part[3], s[i + 2], s[i + 3]);
       }

@@ -169,6 +169,38 @@ __device__ __forceinline__ void add2(float& a, float& b, float x, float y) {  //
       : "+f"(a), "+f"(b) : "f"(x), "f"(y));
 }
 
+// max(a, b, c) in one instruction (three-input form of sm_100).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 2^x for two values on the FMA pipe (no MUFU): x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a degree-5 polynomial (relative error 2.3e-7, the class of ex2.approx), scaled by 2^n
+// through an integer add into the exponent field.  Needs -125 <= x < 128; callers clamp.
+__device__ __forceinline__ void exp2_poly2(float& a, float& b) {
+  asm("{\n\t.reg .b64 x, t, n, f, p, c;\n\t.reg .b32 t0, t1, p0, p1;\n\t"
+      "mov.b64 x, {%0, %1};\n\t"
+      "mov.b64 c, {%2, %2};\n\t"
+      "add.rn.f32x2 t, x, c;\n\t"          // low mantissa bits of t hold n
+      "sub.rn.f32x2 n, t, c;\n\t"
+      "sub.rn.f32x2 f, x, n;\n\t"
+      "mov.b64 p, {%3, %3};\n\t"
+      "mov.b64 c, {%4, %4};\n\tfma.rn.f32x2 p, p, f, c;\n\t"
+      "mov.b64 c, {%5, %5};\n\tfma.rn.f32x2 p, p, f, c;\n\t"
+      "mov.b64 c, {%6, %6};\n\tfma.rn.f32x2 p, p, f, c;\n\t"
+      "mov.b64 c, {%7, %7};\n\tfma.rn.f32x2 p, p, f, c;\n\t"
+      "mov.b64 c, {%8, %8};\n\tfma.rn.f32x2 p, p, f, c;\n\t"
+      "mov.b64 {p0, p1}, p;\n\tmov.b64 {t0, t1}, t;\n\t"
+      "shl.b32 t0, t0, 23;\n\tshl.b32 t1, t1, 23;\n\t"
+      "add.s32 p0, p0, t0;\n\tadd.s32 p1, p1, t1;\n\t"
+      "mov.b32 %0, p0;\n\tmov.b32 %1, p1;\n\t}"
+      : "+f"(a), "+f"(b)
+      : "f"(12582912.0f), "f"(0.0013276288518682122f), "f"(0.009675540030002594f), "f"(0.05550713837146759f),
+        "f"(0.24022120237350464f), "f"(0.6931469440460205f), "f"(1.0000001192092896f));
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }

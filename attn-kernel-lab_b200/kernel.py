@@ -36,7 +36,7 @@ EXPORTS = (
     "akl_prefill_extend", "akl_kv_tile_stats", "akl_kv_means", "akl_kv_scales",
     "akl_kv_transform", "akl_quantize_q", "akl_attention", "akl_attention_dump",
     "akl_merge_states", "akl_prefill_extend_static_scratch",
-    "akl_batch_layout", "akl_batch_plan", "akl_prefill_extend_batch",
+    "akl_batch_layout", "akl_batch_plan", "akl_prefill_extend_batch", "akl_prefill_extend_batch_phases",
 )
 
 AKL_OK = 0
@@ -45,6 +45,7 @@ AKL_ERR_CUDA, AKL_ERR_ALIGN, AKL_ERR_TIMEOUT = -4, -5, -6
 AKL_KV_BF16, AKL_KV_FP16 = 0, 1
 AKL_IDX_I64, AKL_IDX_I32 = 0, 1
 AKL_FLAG_ROTATE, AKL_FLAG_CENTER_K, AKL_FLAG_QK_I8 = 1, 2, 4
+AKL_BATCH_STATS, AKL_BATCH_MEANS, AKL_BATCH_TRANSFORM, AKL_BATCH_ATTENTION, AKL_BATCH_ALL = 1, 2, 4, 8, 15
 
 
 class Plan(ctypes.Structure):
@@ -214,6 +215,8 @@ def load():
         lib.akl_batch_plan.restype = ctypes.c_int
         lib.akl_prefill_extend_batch.argtypes = [ctypes.POINTER(Batch), ctypes.c_void_p]
         lib.akl_prefill_extend_batch.restype = ctypes.c_int
+        lib.akl_prefill_extend_batch_phases.argtypes = [ctypes.POINTER(Batch), ctypes.c_uint32, ctypes.c_void_p]
+        lib.akl_prefill_extend_batch_phases.restype = ctypes.c_int
         _lib = lib
     return _lib
 

@@ -351,14 +351,21 @@ class FP8PrefillBatchWorkspace:
         self._fill(plan.table_host, plan.batch, requests)
         plan.n_requests = len(requests)
 
-    def launch(self, plan: BatchPlan) -> None:
-        """Copy the table to the device and enqueue the four kernels on the current stream."""
+    def upload(self, plan: BatchPlan) -> None:
+        """Copy the table to the device (stream-ordered, from pinned memory)."""
         self._table.copy_(plan.table_host, non_blocking=True)
         if torch.cuda.is_current_stream_capturing():
             self._held.append(plan)      # the graph's copy node reads this host buffer at replay
+
+    def launch(self, plan: BatchPlan, phases: int = _kernel.AKL_BATCH_ALL, upload: bool = True) -> None:
+        """Copy the table to the device and enqueue the batch's kernels on the current stream
+        (`phases`: a subset, AKL_BATCH_* bits, for per-phase timing)."""
+        if upload:
+            self.upload(plan)
         with torch.cuda.device(self.device):
-            code = _kernel.load().akl_prefill_extend_batch(ctypes.byref(plan.batch), _stream(self.device))
-        _kernel.check(code, "akl_prefill_extend_batch")
+            code = _kernel.load().akl_prefill_extend_batch_phases(ctypes.byref(plan.batch), phases,
+                                                                  _stream(self.device))
+        _kernel.check(code, "akl_prefill_extend_batch_phases")
 
 
 def _unswizzle_planes(img: torch.Tensor) -> torch.Tensor:

@@ -245,6 +245,15 @@ int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* requests, in
  * for the same caps, workspace, dtypes and flags. */
 int akl_prefill_extend_batch(const akl_batch_t* b, void* stream);
 
+/* A subset of the batch's launches, in their fixed order, for callers that put their own work
+ * between them and for per-phase timing: the batched counterpart of the phase entry points above. */
+#define AKL_BATCH_STATS 1u      /* tile statistics + Q quantisation */
+#define AKL_BATCH_MEANS 2u      /* channel means, V tile scales, fold arrays */
+#define AKL_BATCH_TRANSFORM 4u  /* K/V centre, rotate, quantise */
+#define AKL_BATCH_ATTENTION 8u
+#define AKL_BATCH_ALL 15u
+int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void* stream);
+
 /* The whole operator (same work and same results as akl_prefill_extend) for callers that cannot
  * allocate device memory -- an engine plugin that is handed no allocator, or a host whose memory
  * pool is frozen after start-up.  The workspace is a 16 MiB array built into the library (held by

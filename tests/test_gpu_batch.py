@@ -104,8 +104,8 @@ def test_native_batch_variants_fp16_pool_int32_index_modes_and_mixed_pools(pkg, 
     assert bws.status() == 0
     for i, (o, ro) in enumerate(zip(res, ref)):
         assert torch.equal(bits(o), bits(ro)), i
-    with pytest.raises(pkg.WorkspaceCapacityError):
-        H.fp8_batch(pkg, reqs + more, workspace=bws, sm_scale=1 / 16, capability=pkg.GENERALIZATION_CAPABILITY)
+    with pytest.raises(pkg.WorkspaceCapacityError):       # five requests of one group, capacity four
+        H.fp8_batch(pkg, reqs + reqs[:2], workspace=bws, sm_scale=1 / 16, capability=pkg.GENERALIZATION_CAPABILITY)
 
 
 def test_graph_of_the_native_batch_follows_a_replanned_table(pkg, cuda):
