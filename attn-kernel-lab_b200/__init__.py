@@ -2,8 +2,8 @@
 
 Same consumer-facing names as the reference package (src/attn_kernel_lab/__init__.py):
 the declared capability surface, the typed error that separates "outside the surface" from
-a defect, and the operator entry points.  The directory name is not a Python identifier, so
-import it through `__graft_entry__.package()` (or `importlib`) as `attn_kernel_lab_b200`.
+a defect, and the operator entry points.  Import it as `attn_kernel_lab_b200` (the one-file module
+of that name beside this directory loads it; the directory name itself is not an identifier).
 """
 from .backend import BackendSettings, make_backend_class
 from .capability import (

@@ -68,7 +68,7 @@ using namespace ptx;
 #define AKL_TRACE_AUX(cond, j_, k) do { } while (0)
 #endif
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 640;
 constexpr int kProducerWarp = 12, kPvWarp = 13, kVProducerWarp = 14, kQkWarp = 15;
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = 32768;
@@ -140,6 +140,23 @@ __device__ __forceinline__ bool wait(const Ctx& c, int slot, uint32_t parity) {
   }
 }
 
+// One arrival for the whole warp: every lane's earlier writes (and fences) are ordered before
+// lane 0's releasing arrive by the warp barrier.  Barrier counts are in warps.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+__device__ __forceinline__ void scale32(uint32_t (&v)[32], float alpha) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+    mul2(x0, x1, alpha);
+    v[i] = __float_as_uint(x0);
+    v[i + 1] = __float_as_uint(x1);
+  }
+}
+
 // Running-maximum hand-off: word = (tiles finished << 32) | float bits of the maximum after
 // them.  The consumer of tile j waits until `tiles finished` reaches j.
 __device__ __forceinline__ void chain_post(uint32_t addr, uint32_t seq, float m) {
@@ -191,58 +208,64 @@ __device__ __forceinline__ float acc_value(uint32_t word) {
   return kI8 ? __int2float_rn(static_cast<int>(word)) : __uint_as_float(word);
 }
 
-// kBatch = false: one work item per CTA, (q tile, head) from the block index, geometry in the
-// kernel parameter.  kBatch = true: a persistent CTA draws (request, head, q tile) items from the
-// request table's list through an atomic counter and keeps the current request's geometry in
-// shared memory; tensor memory is allocated once, the mbarriers are rebuilt per item.
-template <bool kDump, bool kI8, bool kBatch>
-__global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_constant__ Geom g_param, BatchRef bref) {
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_flag;
-  __shared__ int sm_item;
-  __shared__ Geom sm_geom;
-  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
-  float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
-  float2* sm_fin = reinterpret_cast<float2*>(smem_gen + kOffFin);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const Geom& g = kBatch ? sm_geom : g_param;
+// Registers per thread after the per-role re-budgeting (setmaxnreg): the kernel starts with
+// 96 per thread (640 threads x 96 = 61440); the four issuing warps give theirs up, the
+// softmax warpgroups take them.  8*32*120 + 8*32*96 + 4*32*40 = 60416 <= 61440.
+#ifndef AKL_REGS_SOFTMAX
+#define AKL_REGS_SOFTMAX 120
+#define AKL_REGS_CORR 96
+#endif
+constexpr int kRegsSoftmax = AKL_REGS_SOFTMAX, kRegsCorr = AKL_REGS_CORR, kRegsMisc = 40;
+static_assert(8 * 32 * kRegsSoftmax + 8 * 32 * kRegsCorr + 4 * 32 * kRegsMisc <= 640 * 96, "register budget");
 
-  if (tid == 0) abort_flag = 0;
-  if (warp == kProducerWarp) tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
-  int cur_request = -1;
+// What one (q tile, q head) work item needs, derived by every thread for itself.
+struct Item {
+  int qt, h, kvh, m0, ntile, npair;
+};
 
-  for (int iter = 0;; ++iter) {
-  int qt, h;
+struct Shared {
+  uint32_t tmem_slot;
+  int abort_flag;
+  int item;       // batch mode: index of the current work item (or >= n_items: stop)
+  int2 word;      // batch mode: {request, head << 16 | q tile} of the current item
+  Geom geom;      // batch mode: geometry of the current request
+};
+
+// Top of every role's item loop; all 640 threads call it the same number of times.  Returns false
+// when there is no further item.  kBatch = false: the single item comes from the block index.
+// kBatch = true: thread 0 has drawn the item ahead of time (`drawn`), publishes it, and draws the
+// next one so that the atomic's round trip is off the path; the request's geometry is copied to
+// shared memory when the request changes; the mbarriers are invalidated and rebuilt (every async
+// arrival of the previous item has landed: its last MMA was observed before the epilogue).
+template <bool kBatch>
+__device__ __forceinline__ bool begin_item(const Geom& g, const BatchRef& bref, Shared& sh, uint32_t smem, uint8_t* smem_gen,
+                                           int iter, int& cur_request, int& drawn, Item& it) {
+  const int tid = threadIdx.x;
   if (kBatch) {
     BatchHeader* hdr = batch_header(bref);
-    if (tid == 0) sm_item = atomicAdd(&hdr->attn_counter, 1);
-    __syncthreads();                    // every role is done with the previous item; sm_item is set
-    const int item = sm_item;
-    if (item >= hdr->n_attn_items || abort_flag != 0) break;     // CTA-uniform
-    const int2 w = __ldg(reinterpret_cast<const int2*>(bref.table + bref.off_items) + item);
-    h = w.y >> 16;
-    qt = w.y & 0xFFFF;
+    if (tid == 0) {
+      sh.item = drawn;
+      if (drawn < hdr->n_attn_items) sh.word = __ldg(reinterpret_cast<const int2*>(bref.table + bref.off_items) + drawn);
+    }
+    __syncthreads();                    // every role is done with the previous item; the new one is published
+    const int item = sh.item;
+    if (item >= hdr->n_attn_items || sh.abort_flag != 0) return false;     // CTA-uniform
+    const int2 w = sh.word;
+    it.h = w.y >> 16;
+    it.qt = w.y & 0xFFFF;
     if (w.x != cur_request) {
       const uint32_t* src = reinterpret_cast<const uint32_t*>(bref.table + bref.off_geoms + static_cast<size_t>(w.x) * sizeof(Geom));
-      uint32_t* dst = reinterpret_cast<uint32_t*>(&sm_geom);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&sh.geom);
       if (tid < static_cast<int>(sizeof(Geom) / 4)) dst[tid] = src[tid];
       cur_request = w.x;
     }
   } else {
-    if (iter > 0) break;
-    qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
-    h = blockIdx.y;
+    if (iter > 0) return false;
+    it.qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // deepest tiles first
+    it.h = blockIdx.y;
   }
-
-  Ctx ctx{smem + kOffBar, nullptr, &abort_flag};
   if (tid == 0) {
-    const uint32_t b = ctx.bars;
+    const uint32_t b = smem + kOffBar;
     if (iter > 0) {
       for (int i = 0; i < B_COUNT; ++i) mbar_inval(b + i * 8);
     }
@@ -253,150 +276,197 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       mbar_init(b + (B_VFULL + i) * 8, 1);
       mbar_init(b + (B_VEMPTY + i) * 8, 1);
       mbar_init(b + (B_SFULL + i) * 8, 1);
-      mbar_init(b + (B_SEMPTY + i) * 8, 256);
+      mbar_init(b + (B_SEMPTY + i) * 8, 8);
     }
     for (int i = 0; i < 4; ++i) {
-      mbar_init(b + (B_PFULL + i) * 8, 128);
-      mbar_init(b + (B_AREADY + i) * 8, 128);
+      mbar_init(b + (B_PFULL + i) * 8, 4);
+      mbar_init(b + (B_AREADY + i) * 8, 4);
     }
     for (int i = 0; i < 4; ++i) mbar_init(b + (B_PEMPTY + i) * 8, 1);
     mbar_init(b + B_PVDONE * 8, 1);
-    mbar_init(b + B_OREADY * 8, 128);
+    mbar_init(b + B_OREADY * 8, 8);
     mbar_init(b + B_ALLDONE * 8, 1);
     mbar_init_fence();
     fence_async_smem();
   }
-  if (kBatch) __syncthreads();          // the staged geometry is visible
-  ctx.status = g.status;
-  const int kvh = h / (g.Hq / g.Hkv);
-  const int m0 = qt * kQTile;
-
-  // keys this CTA visits, in local (this call's) positions
-  long long hi_ll = static_cast<long long>(g.prefix) + m0 + kQTile - g.kv_pos0;
+  if (kBatch) {
+    __syncthreads();                    // the staged geometry is visible
+    if (tid == 0) drawn = atomicAdd(&batch_header(bref)->attn_counter, 1);
+  }
+  it.kvh = it.h / (g.Hq / g.Hkv);
+  it.m0 = it.qt * kQTile;
+  // keys this item visits, in local (this call's) positions
+  long long hi_ll = static_cast<long long>(g.prefix) + it.m0 + kQTile - g.kv_pos0;
   const int hi = static_cast<int>(hi_ll < 0 ? 0 : (hi_ll > g.N ? g.N : hi_ll));
-  const int ntile = (hi + kTile - 1) / kTile;
-  const int npair = (ntile + 1) / 2;
-
+  it.ntile = (hi + kTile - 1) / kTile;
+  it.npair = (it.ntile + 1) / 2;
   if (tid < 128) {
-    sm_vmean[tid] = g.vmean[kvh * kD + tid];
-    sm_vmean[tid + 128] = g.vmean[kvh * kD + tid + 128];
+    float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
+    sm_vmean[tid] = g.vmean[it.kvh * kD + tid];
+    sm_vmean[tid + 128] = g.vmean[it.kvh * kD + tid + 128];
     chain_post(smem + kOffChain + tid * 8, 0u, -INFINITY);      // "zero tiles finished, max = -inf"
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  return true;
+}
 
-  if (warp == kProducerWarp) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0 && ntile > 0) {
-      const uint8_t* qsrc = g.q8 + (static_cast<size_t>(h) * g.mtiles_cap + qt) * kImageBytes;
-      const uint8_t* ksrc = g.k8 + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
-      mbar_expect_tx(ctx.bars + B_QFULL * 8, kImageBytes);
-      bulk_g2s(smem + kOffQ, qsrc, kImageBytes, ctx.bars + B_QFULL * 8);
-      for (int u = 0; u < npair; ++u) {
-        const int s = u & 1, n = u >> 1;
-        if (n >= 1 && !wait(ctx, B_KEMPTY + s, (n - 1) & 1)) break;
-        mbar_expect_tx(ctx.bars + (B_KFULL + s) * 8, kImageBytes);
-        bulk_g2s(smem + kOffK + s * 32768, ksrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
-                 ctx.bars + (B_KFULL + s) * 8);
+// kBatch = false: one work item per CTA, (q tile, head) from the block index, geometry in the
+// kernel parameter.  kBatch = true: a persistent CTA draws (request, head, q tile) items from the
+// request table's list through an atomic counter and keeps the current request's geometry in
+// shared memory; tensor memory is allocated once, the mbarriers are rebuilt per item.
+// Every role runs its own loop over the items, so that each loop is compiled for its own
+// register budget.
+template <bool kDump, bool kI8, bool kBatch>
+__global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_constant__ Geom g_param, const __grid_constant__ BatchRef bref) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Shared sh;
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+  float* sm_vmean = reinterpret_cast<float*>(smem_gen + kOffVmean);
+  float2* sm_fin = reinterpret_cast<float2*>(smem_gen + kOffFin);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const Geom& g = kBatch ? sh.geom : g_param;
+
+  if (tid == 0) sh.abort_flag = 0;
+  if (warp == kProducerWarp) tmem_alloc(smem_u32(&sh.tmem_slot), kTmemCols);
+  int drawn = 0;
+  if (kBatch && tid == 0) drawn = atomicAdd(&batch_header(bref)->attn_counter, 1);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_slot;
+  int cur_request = -1;
+  Ctx ctx{smem + kOffBar, nullptr, &sh.abort_flag};
+  Item it;
+
+  if (warp >= 12 && warp < 16) {
+    // ================================================================ issuing warps
+    reg_dealloc<kRegsMisc>();
+    for (int iter = 0; begin_item<kBatch>(g, bref, sh, smem, smem_gen, iter, cur_request, drawn, it); ++iter) {
+      ctx.status = g.status;
+      const int ntile = it.ntile, npair = it.npair;
+      if (lane != 0 || ntile == 0) continue;
+      if (warp == kProducerWarp) {
+        // ---------------------------------------------------------- Q and K copies
+        const uint8_t* qsrc = g.q8 + (static_cast<size_t>(it.h) * g.mtiles_cap + it.qt) * kImageBytes;
+        const uint8_t* ksrc = g.k8 + static_cast<size_t>(it.kvh) * g.npairs_cap * kImageBytes;
+        mbar_expect_tx(ctx.bars + B_QFULL * 8, kImageBytes);
+        bulk_g2s(smem + kOffQ, qsrc, kImageBytes, ctx.bars + B_QFULL * 8);
+        for (int u = 0; u < npair; ++u) {
+          const int s = u & 1, n = u >> 1;
+          if (n >= 1 && !wait(ctx, B_KEMPTY + s, (n - 1) & 1)) break;
+          mbar_expect_tx(ctx.bars + (B_KFULL + s) * 8, kImageBytes);
+          bulk_g2s(smem + kOffK + s * 32768, ksrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
+                   ctx.bars + (B_KFULL + s) * 8);
+        }
+      } else if (warp == kVProducerWarp) {
+        // ---------------------------------------------------------- V^T copies
+        const uint8_t* vsrc = g.v8t + static_cast<size_t>(it.kvh) * g.npairs_cap * kImageBytes;
+        for (int u = 0; u < npair; ++u) {
+          const int s = u & 1, n = u >> 1;
+          if (n >= 1 && !wait(ctx, B_VEMPTY + s, (n - 1) & 1)) break;
+          mbar_expect_tx(ctx.bars + (B_VFULL + s) * 8, kImageBytes);
+          bulk_g2s(smem + kOffV + s * 32768, vsrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
+                   ctx.bars + (B_VFULL + s) * 8);
+        }
+      } else if (warp == kQkWarp) {
+        // ---------------------------------------------------------- QK^T issuer
+        const uint32_t q_lo = desc_lo(smem + kOffQ);
+        bool ok = wait(ctx, B_QFULL, 0);
+        for (int u = 0; ok && u < npair; ++u) {
+          const int b = u & 1, n = u >> 1;
+          ok = wait(ctx, B_KFULL + b, n & 1);
+          if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + b, (n - 1) & 1);   // both groups have read S(u-2)
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk<kI8>(q_lo, desc_lo(smem + kOffK + b * 32768), tmem + kColS + b * 128);
+          tc_commit(ctx.bars + (B_SFULL + b) * 8);
+          tc_commit(ctx.bars + (B_KEMPTY + b) * 8);
+        }
+      } else {
+        // ---------------------------------------------------------- PV issuer
+        bool ok = true;
+        for (int j = 0; ok && j < ntile; ++j) {
+          const int u = j >> 1, c = j & 1, b = u & 1, par = (u >> 1) & 1;
+          if (c == 0) ok = wait(ctx, B_VFULL + b, par);
+          ok = ok && wait(ctx, B_PFULL + b * 2 + c, par) && wait(ctx, B_OREADY, j & 1);
+          if (!ok) break;
+          tc_fence_after();
+          AKL_TRACE_AUX(true, j, 3);
+          issue_pv(desc_lo(smem + kOffP + b * 16384 + c * 64), desc_lo(smem + kOffV + b * 32768 + c * 64),
+                   tmem + kColO, j > 0 ? 1u : 0u);
+          tc_commit(ctx.bars + B_PVDONE * 8);
+          tc_commit(ctx.bars + (B_PEMPTY + b * 2 + c) * 8);
+          AKL_TRACE_AUX(true, j, 4);
+          if (c == 1 || j == ntile - 1) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
+        }
+        if (ok) tc_commit(ctx.bars + B_ALLDONE * 8);
       }
     }
-  } else if (warp == kVProducerWarp) {
-    if (lane == 0 && ntile > 0) {
-      const uint8_t* vsrc = g.v8t + static_cast<size_t>(kvh) * g.npairs_cap * kImageBytes;
-      for (int u = 0; u < npair; ++u) {
-        const int s = u & 1, n = u >> 1;
-        if (n >= 1 && !wait(ctx, B_VEMPTY + s, (n - 1) & 1)) break;
-        mbar_expect_tx(ctx.bars + (B_VFULL + s) * 8, kImageBytes);
-        bulk_g2s(smem + kOffV + s * 32768, vsrc + static_cast<size_t>(u) * kImageBytes, kImageBytes,
-                 ctx.bars + (B_VFULL + s) * 8);
-      }
-    }
-  } else if (warp == kQkWarp) {
-    // ------------------------------------------------------------ QK^T issuer
-    if (lane == 0 && ntile > 0) {
-      const uint32_t q_lo = desc_lo(smem + kOffQ);
-      bool ok = wait(ctx, B_QFULL, 0);
-      for (int u = 0; ok && u < npair; ++u) {
-        const int b = u & 1, n = u >> 1;
-        ok = wait(ctx, B_KFULL + b, n & 1);
-        if (ok && n >= 1) ok = wait(ctx, B_SEMPTY + b, (n - 1) & 1);   // both groups have read S(u-2)
-        if (!ok) break;
-        tc_fence_after();
-        issue_qk<kI8>(q_lo, desc_lo(smem + kOffK + b * 32768), tmem + kColS + b * 128);
-        tc_commit(ctx.bars + (B_SFULL + b) * 8);
-        tc_commit(ctx.bars + (B_KEMPTY + b) * 8);
-      }
-    }
-  } else if (warp == kPvWarp) {
-    // ------------------------------------------------------------ PV issuer
-    if (lane == 0 && ntile > 0) {
-      bool ok = true;
-      for (int j = 0; ok && j < ntile; ++j) {
-        const int u = j >> 1, c = j & 1, b = u & 1, par = (u >> 1) & 1;
-        if (c == 0) ok = wait(ctx, B_VFULL + b, par);
-        ok = ok && wait(ctx, B_PFULL + b * 2 + c, par) && wait(ctx, B_OREADY, j & 1);
-        if (!ok) break;
-        tc_fence_after();
-        AKL_TRACE_AUX(true, j, 3);
-        issue_pv(desc_lo(smem + kOffP + b * 16384 + c * 64), desc_lo(smem + kOffV + b * 32768 + c * 64),
-                 tmem + kColO, j > 0 ? 1u : 0u);
-        tc_commit(ctx.bars + B_PVDONE * 8);
-        tc_commit(ctx.bars + (B_PEMPTY + b * 2 + c) * 8);
-        AKL_TRACE_AUX(true, j, 4);
-        if (c == 1 || j == ntile - 1) tc_commit(ctx.bars + (B_VEMPTY + b) * 8);
-      }
-      if (ok) tc_commit(ctx.bars + B_ALLDONE * 8);
-    }
-  } else if (warp >= 8 && warp < 12) {
-    // ------------------------------------------------------------ correction warpgroup
+  } else if (warp >= 8) {
+    // ================================================================ correction warpgroups
+    // warps 8-11 own O columns 0-127, warps 16-19 columns 128-255
+    if (kRegsCorr > 96) reg_alloc<kRegsCorr>();
     const int row = tid & 127;
+    const uint32_t col0 = kColO + (warp >= 16 ? 128u : 0u);
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const float* sm_alpha = reinterpret_cast<const float*>(smem_gen + kOffAlpha);
-    for (int j = 0; j < ntile; ++j) {
-      if (!wait(ctx, B_AREADY + (j & 3), (j >> 2) & 1)) break;
-      AKL_TRACE_AUX(row == 0, j, 0);
-      const float alpha = sm_alpha[(j & 3) * 128 + row];
-      if (j > 0) {
-        if (!wait(ctx, B_PVDONE, (j - 1) & 1)) break;          // every phase, in order
-        AKL_TRACE_AUX(row == 0, j, 1);
-        __syncwarp();
-        // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          tc_fence_after();
-#pragma unroll 1
-          for (int ch = 0; ch < 8; ch += 2) {
+    for (int iter = 0; begin_item<kBatch>(g, bref, sh, smem, smem_gen, iter, cur_request, drawn, it); ++iter) {
+      ctx.status = g.status;
+      const int ntile = it.ntile;
+      for (int j = 0; j < ntile; ++j) {
+        if (!wait(ctx, B_AREADY + (j & 3), (j >> 2) & 1)) break;
+        AKL_TRACE_AUX(tid == 256, j, 0);
+        const float alpha = sm_alpha[(j & 3) * 128 + row];
+        if (j > 0) {
+          if (!wait(ctx, B_PVDONE, (j - 1) & 1)) break;          // every phase, in order
+          AKL_TRACE_AUX(tid == 256, j, 1);
+          __syncwarp();
+          // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            tc_fence_after();
             uint32_t oa[32], ob[32];
-            tmem_ld32(lane_base + kColO + ch * 32, oa);
-            tmem_ld32(lane_base + kColO + ch * 32 + 32, ob);
+            tmem_ld32(lane_base + col0, oa);
+            tmem_ld32(lane_base + col0 + 32, ob);
             tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float x0 = __uint_as_float(oa[i]), x1 = __uint_as_float(oa[i + 1]);
-              float y0 = __uint_as_float(ob[i]), y1 = __uint_as_float(ob[i + 1]);
-              mul2(x0, x1, alpha);
-              mul2(y0, y1, alpha);
-              oa[i] = __float_as_uint(x0); oa[i + 1] = __float_as_uint(x1);
-              ob[i] = __float_as_uint(y0); ob[i + 1] = __float_as_uint(y1);
-            }
-            tmem_st32(lane_base + kColO + ch * 32, oa);
-            tmem_st32(lane_base + kColO + ch * 32 + 32, ob);
+            scale32(oa, alpha);
+            tmem_st32(lane_base + col0, oa);
+#ifdef AKL_RESCALE_PIPE
+            tmem_ld32(lane_base + col0 + 64, oa);        // next round's load flies during the multiply below
+#endif
+            scale32(ob, alpha);
+            tmem_st32(lane_base + col0 + 32, ob);
+#ifndef AKL_RESCALE_PIPE
+            tmem_ld32(lane_base + col0 + 64, oa);
+#endif
+            tmem_ld32(lane_base + col0 + 96, ob);
+            tmem_wait_ld();
+            scale32(oa, alpha);
+            tmem_st32(lane_base + col0 + 64, oa);
+            scale32(ob, alpha);
+            tmem_st32(lane_base + col0 + 96, ob);
+            tmem_wait_st();
+            tc_fence_before();
           }
-          tmem_wait_st();
-          tc_fence_before();
         }
+        warp_arrive(ctx.bars + B_OREADY * 8, lane);
+        AKL_TRACE_AUX(tid == 256, j, 2);
       }
-      mbar_arrive(ctx.bars + B_OREADY * 8);
-      AKL_TRACE_AUX(row == 0, j, 2);
     }
   } else {
-    // ------------------------------------------------------------ softmax warpgroups
+    // ================================================================ softmax warpgroups
+    reg_alloc<kRegsSoftmax>();
     const int wg = warp >> 2;                  // 0: even tiles, 1: odd tiles
     const int row = tid & 127;                 // query row inside the tile == TMEM lane
-    const int grow = m0 + row;
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const uint32_t chain = smem + kOffChain + row * 8;
     float* sm_alpha = reinterpret_cast<float*>(smem_gen + kOffAlpha);
+    for (int iter = 0; begin_item<kBatch>(g, bref, sh, smem, smem_gen, iter, cur_request, drawn, it); ++iter) {
+    ctx.status = g.status;
+    const int ntile = it.ntile, h = it.h, kvh = it.kvh, qt = it.qt;
+    const int grow = it.m0 + row;
     long long lim_ll = static_cast<long long>(g.prefix) + grow - g.kv_pos0;
     const int limit = static_cast<int>(lim_ll > g.N - 1 ? g.N - 1 : lim_ll);   // last visible local key (may be < 0)
     const float qs = g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
@@ -441,7 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       }
       AKL_TRACE_POINT(0);
       tc_fence_before();
-      mbar_arrive(ctx.bars + (B_SEMPTY + b) * 8);      // 256 arrivals free the S buffer
+      warp_arrive(ctx.bars + (B_SEMPTY + b) * 8, lane);      // the eight softmax warps free the S buffer
       if (kDump) {
         float* dst = g.dbg_s + ((((static_cast<size_t>(h) * g.mtiles + qt) * g.nt + j) * kQTile + row) * kTile);
 #pragma unroll
@@ -501,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       // alpha of this tile goes to the correction group
       const float alpha_o = (m_prev == -INFINITY) ? 0.f : ex2((m_prev - m_new) * kLog2e);
       sm_alpha[(j & 3) * 128 + row] = alpha_o;
-      mbar_arrive(ctx.bars + (B_AREADY + (j & 3)) * 8);
+      warp_arrive(ctx.bars + (B_AREADY + (j & 3)) * 8, lane);
       const float alpha_l = (m_own == -INFINITY) ? 0.f : ex2((m_own - m_new) * kLog2e);
       const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
       m_own = m_new;
@@ -551,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       fence_async_smem();
       AKL_TRACE_POINT(4);
 
-      mbar_arrive(ctx.bars + (B_PFULL + b * 2 + c) * 8);
+      warp_arrive(ctx.bars + (B_PFULL + b * 2 + c) * 8, lane);
       AKL_TRACE_POINT(6);
     }
 
@@ -560,7 +630,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
     sm_fin[wg * 128 + row] = make_float2(m_own, l_own);
     if (ok && ntile > 0) ok = wait(ctx, B_ALLDONE, 0);
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    ok = __all_sync(0xffffffffu, ok) && (abort_flag == 0);
+    ok = __all_sync(0xffffffffu, ok) && (sh.abort_flag == 0);
     if (ok) {
       tc_fence_after();
       const float2 f0 = sm_fin[row], f1 = sm_fin[128 + row];
@@ -602,10 +672,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       }
       tc_fence_before();
     }
+    }   // items
   }
-
-  if (!kBatch) break;
-  }   // work items
 
   __syncthreads();
   if (warp == kProducerWarp) {

@@ -62,6 +62,18 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// ---- per-warpgroup register re-budgeting ------------------------------------------
+// All four warps of a warpgroup execute the same instruction.  `inc` waits until the CTA's pool
+// holds enough registers that other warpgroups released with `dec`; the budgets must add up.
+template <int kRegs>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---- tensor memory ----------------------------------------------------------
 // One warp, all lanes.  ncols: power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {

@@ -186,8 +186,8 @@ def load():
             return _lib
         if not LIB_PATH.exists():
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python -c \"import __graft_entry__ as g; "
-                "g.build()\"` (needs nvcc).  This operator has no CPU or tensor-library fallback."
+                f"{LIB_PATH} is missing: build it with `python -c \"import attn_kernel_lab_b200 as a; "
+                "a.build()\"` (needs nvcc).  This operator has no CPU or tensor-library fallback."
             )
         lib = ctypes.CDLL(str(LIB_PATH))
         missing = [name for name in EXPORTS if not hasattr(lib, name)]
