@@ -460,7 +460,14 @@ int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void*
   if ((phases & AKL_BATCH_STATS) && (rc = launch_batch_stats(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
   if ((phases & AKL_BATCH_MEANS) && (rc = launch_batch_means(ref, b->caps.kv_heads, s)) != AKL_OK) return rc;
   if ((phases & AKL_BATCH_TRANSFORM) && (rc = launch_batch_transform(ref, b->kv_dtype, b->idx_dtype, sms, s)) != AKL_OK) return rc;
-  if (phases & AKL_BATCH_ATTENTION) return launch_batch_attention(ref, (b->flags & AKL_FLAG_QK_I8) != 0, sms, s);
+  if (phases & AKL_BATCH_ATTENTION) {
+    if (!(phases & AKL_BATCH_MEANS)) {
+      // the means launch rewinds the attention work counter; without it, do that here
+      cudaError_t e = cudaMemsetAsync(&batch_header(ref)->attn_counter, 0, sizeof(int32_t), s);
+      if (e != cudaSuccess) { note_cuda_error(e, "cudaMemsetAsync(work counter)"); return AKL_ERR_CUDA; }
+    }
+    return launch_batch_attention(ref, (b->flags & AKL_FLAG_QK_I8) != 0, sms, s);
+  }
   return AKL_OK;
 }
 

@@ -15,11 +15,12 @@
 // per 64-key tile, in tile order -- the tile sequence is part of the operator because P is
 // rounded against the running maximum.
 //
-// CTA = 16 warps:
+// CTA = 20 warps, every role with its own loop over the CTA's work items:
 //   warps 0-3   softmax warpgroup 0: even 64-key tiles  } thread i of a group owns query row i,
 //   warps 4-7   softmax warpgroup 1: odd  64-key tiles  } which is TMEM lane i
-//   warps 8-11  correction warpgroup: multiplies O by alpha between two PV MMAs when a row's
-//               running maximum moved, so the softmax groups never wait for the tensor pipe,
+//   warps 8-11  correction warpgroup A: O columns 0-127   } multiply O by alpha between two PV MMAs
+//   warps 16-19 correction warpgroup B: O columns 128-255 } when a row's running maximum moved, so
+//               that the softmax groups never wait for the tensor pipe,
 //   warp  12    lane 0 issues the Q and K bulk copies; the warp owns TMEM allocation,
 //   warp  14    lane 0 issues the V^T bulk copies (its own thread, so that a K tile whose stage
 //               is free is never queued behind a wait for a V stage),
@@ -27,12 +28,20 @@
 //   warp  15    lane 0 issues the QK^T MMAs (as soon as an S buffer has been read out).
 // The two issuing threads sit on different warp schedulers and never wait for each other's
 // inputs, so the tensor pipe always has the QK^T of a later pair to run while the correction of
-// the next tile is in flight.
-// The two groups alternate tiles so that two warps share each scheduler and hide each other's
-// latencies; the running row maximum is the only state that must travel from one tile to the
-// next, and it is handed from group to group through a 64-bit (sequence, value) word per row in
-// shared memory.  Each group keeps its own partial l against its own last maximum; the two
+// the next tile is in flight.  (One thread issuing both kinds was measured: an MMA costs its
+// issuing thread about a hundred cycles, and eight QK^T issues in front of a PV lengthen the
+// PV -> rescale -> PV chain that sets the tile period.)
+// Registers are re-budgeted per role (setmaxnreg): the kernel starts at 96 per thread, the issuing
+// warps drop to 40 and the softmax warpgroups take 120.
+// The two softmax groups alternate tiles so that two warps share each scheduler and hide each
+// other's latencies; the running row maximum is the only state that must travel from one tile
+// to the next, and it is handed from group to group through a 64-bit (sequence, value) word per
+// row in shared memory.  Each group keeps its own partial l against its own last maximum; the two
 // are combined once, in the epilogue.
+//
+// Work items: one (q tile, q head) per CTA from the block index, or -- the batched entry -- a
+// persistent CTA per SM that draws (request, q head, q tile) items from the request table
+// through an atomic counter (the next item is drawn while the current one runs).
 //
 // Shared memory: Q tile 32 KiB; K and V^T 128-key pair tiles, two stages each (2 x 64 KiB);
 // P 2 x 16 KiB.  Tensor memory (512 columns): O = columns 0-255, S ping-pong = 256-383 /
@@ -69,17 +78,17 @@ using namespace ptx;
 #endif
 
 constexpr int kThreads = 640;
-constexpr int kProducerWarp = 12, kPvWarp = 13, kVProducerWarp = 14, kQkWarp = 15;
+constexpr int kProducerWarp = 12, kVProducerWarp = 14, kQkWarp = 15;   // warp 13 issues the PV MMAs
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = 32768;
 constexpr uint32_t kOffV = kOffK + 2 * 32768;
 constexpr uint32_t kOffP = kOffV + 2 * 32768;
 constexpr uint32_t kOffBar = kOffP + 2 * 16384;      // 196608
-constexpr uint32_t kOffVmean = kOffBar + 256;        // 256 floats
+constexpr uint32_t kOffVmean = kOffBar + 512;        // 256 floats
 constexpr uint32_t kOffChain = kOffVmean + 1024;     // 128 x u64 running-max hand-off words
 constexpr uint32_t kOffFin = kOffChain + 1024;       // [2][128] (m, l) pairs for the epilogue
-constexpr uint32_t kOffAlpha = kOffFin + 2048;       // [4][128] floats: alpha of tile j in slot j & 3
-constexpr uint32_t kSmemBytes = kOffAlpha + 2048 + 1024;   // + alignment slack
+constexpr uint32_t kOffAlpha = kOffFin + 2048;       // [8][128] floats: alpha of tile j in slot j & 7
+constexpr uint32_t kSmemBytes = kOffAlpha + 4096 + 1024;   // + alignment slack
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256;
 constexpr uint32_t kIdescQK = idesc_e4m3(128, 128);
@@ -101,10 +110,10 @@ enum {
   B_PFULL = 13,   // [2][2]
   B_PVDONE = 17,  // one phase per tile; only the correction group waits on it, every tile
   B_ALLDONE = 18,
-  B_AREADY = 19,  // [4] alpha of tile j published (slot j & 3)
+  B_AREADY = 28,  // [8] alpha of tile j published (slot j & 7)
   B_OREADY = 23,  // O carries alpha_j: PV(j) may be issued
   B_PEMPTY = 24,  // [2][2] PV(j) has read P slot (j>>1)&1, j&1 (and the correction of tile j is over)
-  B_COUNT = 28
+  B_COUNT = 36
 };
 
 struct Ctx {
@@ -143,8 +152,7 @@ __device__ __forceinline__ bool wait(const Ctx& c, int slot, uint32_t parity) {
 // One arrival for the whole warp: every lane's earlier writes (and fences) are ordered before
 // lane 0's releasing arrive by the warp barrier.  Barrier counts are in warps.
 __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
+  mbar_arrive(bar);
 }
 
 __device__ __forceinline__ void scale32(uint32_t (&v)[32], float alpha) {
@@ -211,12 +219,9 @@ __device__ __forceinline__ float acc_value(uint32_t word) {
 // Registers per thread after the per-role re-budgeting (setmaxnreg): the kernel starts with
 // 96 per thread (640 threads x 96 = 61440); the four issuing warps give theirs up, the
 // softmax warpgroups take them.  8*32*120 + 8*32*96 + 4*32*40 = 60416 <= 61440.
-#ifndef AKL_REGS_SOFTMAX
-#define AKL_REGS_SOFTMAX 120
-#define AKL_REGS_CORR 96
-#endif
-constexpr int kRegsSoftmax = AKL_REGS_SOFTMAX, kRegsCorr = AKL_REGS_CORR, kRegsMisc = 40;
-static_assert(8 * 32 * kRegsSoftmax + 8 * 32 * kRegsCorr + 4 * 32 * kRegsMisc <= 640 * 96, "register budget");
+constexpr int kRegsStart = 96, kRegsSoftmax = 120, kRegsMisc = 40;    // the correction warps keep 96
+static_assert(8 * 32 * kRegsSoftmax + 8 * 32 * kRegsStart + 4 * 32 * kRegsMisc <= kThreads * kRegsStart,
+              "register budget: an increase waits for registers other warps never release");
 
 // What one (q tile, q head) work item needs, derived by every thread for itself.
 struct Item {
@@ -276,15 +281,13 @@ __device__ __forceinline__ bool begin_item(const Geom& g, const BatchRef& bref, 
       mbar_init(b + (B_VFULL + i) * 8, 1);
       mbar_init(b + (B_VEMPTY + i) * 8, 1);
       mbar_init(b + (B_SFULL + i) * 8, 1);
-      mbar_init(b + (B_SEMPTY + i) * 8, 8);
+      mbar_init(b + (B_SEMPTY + i) * 8, 256);
     }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(b + (B_PFULL + i) * 8, 4);
-      mbar_init(b + (B_AREADY + i) * 8, 4);
-    }
+    for (int i = 0; i < 4; ++i) mbar_init(b + (B_PFULL + i) * 8, 128);
+    for (int i = 0; i < 8; ++i) mbar_init(b + (B_AREADY + i) * 8, 128);
     for (int i = 0; i < 4; ++i) mbar_init(b + (B_PEMPTY + i) * 8, 1);
     mbar_init(b + B_PVDONE * 8, 1);
-    mbar_init(b + B_OREADY * 8, 8);
+    mbar_init(b + B_OREADY * 8, 256);
     mbar_init(b + B_ALLDONE * 8, 1);
     mbar_init_fence();
     fence_async_smem();
@@ -388,15 +391,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       } else {
         // ---------------------------------------------------------- PV issuer
         bool ok = true;
+        const uint32_t p_base = desc_lo(smem + kOffP), v_base = desc_lo(smem + kOffV);
         for (int j = 0; ok && j < ntile; ++j) {
           const int u = j >> 1, c = j & 1, b = u & 1, par = (u >> 1) & 1;
+          const uint32_t p_lo = p_base + ((b * 16384 + c * 64) >> 4), v_lo = v_base + ((b * 32768 + c * 64) >> 4);
+          const uint32_t acc = j > 0 ? 1u : 0u;
           if (c == 0) ok = wait(ctx, B_VFULL + b, par);
           ok = ok && wait(ctx, B_PFULL + b * 2 + c, par) && wait(ctx, B_OREADY, j & 1);
           if (!ok) break;
           tc_fence_after();
           AKL_TRACE_AUX(true, j, 3);
-          issue_pv(desc_lo(smem + kOffP + b * 16384 + c * 64), desc_lo(smem + kOffV + b * 32768 + c * 64),
-                   tmem + kColO, j > 0 ? 1u : 0u);
+          issue_pv(p_lo, v_lo, tmem + kColO, acc);
           tc_commit(ctx.bars + B_PVDONE * 8);
           tc_commit(ctx.bars + (B_PEMPTY + b * 2 + c) * 8);
           AKL_TRACE_AUX(true, j, 4);
@@ -408,7 +413,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
   } else if (warp >= 8) {
     // ================================================================ correction warpgroups
     // warps 8-11 own O columns 0-127, warps 16-19 columns 128-255
-    if (kRegsCorr > 96) reg_alloc<kRegsCorr>();
     const int row = tid & 127;
     const uint32_t col0 = kColO + (warp >= 16 ? 128u : 0u);
     const uint32_t lane_base = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -417,15 +421,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       ctx.status = g.status;
       const int ntile = it.ntile;
       for (int j = 0; j < ntile; ++j) {
-        if (!wait(ctx, B_AREADY + (j & 3), (j >> 2) & 1)) break;
+        if (!wait(ctx, B_AREADY + (j & 7), (j >> 3) & 1)) break;
         AKL_TRACE_AUX(tid == 256, j, 0);
-        const float alpha = sm_alpha[(j & 3) * 128 + row];
+        const float alpha = sm_alpha[(j & 7) * 128 + row];
         if (j > 0) {
+          // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched (decided
+          // before the wait, so that nothing but the fence stands between PV(j-1) and the loads)
+          const bool rescale = __any_sync(0xffffffffu, alpha != 1.f);
           if (!wait(ctx, B_PVDONE, (j - 1) & 1)) break;          // every phase, in order
           AKL_TRACE_AUX(tid == 256, j, 1);
-          __syncwarp();
-          // exact rescale skip: alpha == 1 for every row of the warp leaves O untouched
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          if (rescale) {
             tc_fence_after();
             uint32_t oa[32], ob[32];
             tmem_ld32(lane_base + col0, oa);
@@ -433,14 +438,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
             tmem_wait_ld();
             scale32(oa, alpha);
             tmem_st32(lane_base + col0, oa);
-#ifdef AKL_RESCALE_PIPE
-            tmem_ld32(lane_base + col0 + 64, oa);        // next round's load flies during the multiply below
-#endif
             scale32(ob, alpha);
             tmem_st32(lane_base + col0 + 32, ob);
-#ifndef AKL_RESCALE_PIPE
             tmem_ld32(lane_base + col0 + 64, oa);
-#endif
             tmem_ld32(lane_base + col0 + 96, ob);
             tmem_wait_ld();
             scale32(oa, alpha);
@@ -570,8 +570,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       AKL_TRACE_POINT(2);
       // alpha of this tile goes to the correction group
       const float alpha_o = (m_prev == -INFINITY) ? 0.f : ex2((m_prev - m_new) * kLog2e);
-      sm_alpha[(j & 3) * 128 + row] = alpha_o;
-      warp_arrive(ctx.bars + (B_AREADY + (j & 3)) * 8, lane);
+      sm_alpha[(j & 7) * 128 + row] = alpha_o;
+      warp_arrive(ctx.bars + (B_AREADY + (j & 7)) * 8, lane);
       const float alpha_l = (m_own == -INFINITY) ? 0.f : ex2((m_own - m_new) * kLog2e);
       const float pc = (m_new == -INFINITY) ? -INFINITY : (kLog2_448 + t_l2r) - m_new * kLog2e;
       m_own = m_new;
