@@ -471,6 +471,12 @@ int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void*
   return AKL_OK;
 }
 
+int akl_selftest_exact_division(const float* scales, int32_t n_scales, uint64_t* mismatches, void* stream) {
+  if (scales == nullptr || mismatches == nullptr || n_scales < 1 || n_scales > 65535) return AKL_ERR_INVALID;
+  return launch_exact_division_selftest(scales, n_scales, reinterpret_cast<unsigned long long*>(mismatches),
+                                        static_cast<cudaStream_t>(stream));
+}
+
 int akl_merge_states(const akl_merge_t* m, void* stream) {
   if (m == nullptr || m->parts_o == nullptr || m->parts_lse == nullptr || m->out == nullptr) return AKL_ERR_INVALID;
   return launch_merge(*m, static_cast<cudaStream_t>(stream));

@@ -140,35 +140,131 @@ __device__ __forceinline__ uint32_t cvt_qk_x4(bool i8, float a, float b, float c
   return i8 ? cvt_s8x4(a, b, c, d) : cvt_e4m3x4(a, b, c, d);
 }
 
+// ---- packed fp32 pairs ------------------------------------------------------------------
+// One issue slot for two IEEE round-to-nearest operations; bit-identical to the scalar forms.
+// The preprocessing kernels are bound by instruction issue (a 256-point rotation and an exact
+// division per element), so halving the arithmetic instruction count is what speeds them up.
+struct f2 { unsigned long long v; };
+__device__ __forceinline__ f2 pack2(float a, float b) {
+  f2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f2 p, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(p.v));
+}
+__device__ __forceinline__ f2 add2p(f2 a, f2 b) {
+  f2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ f2 sub2p(f2 a, f2 b) {
+  f2 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ f2 mul2p(f2 a, f2 b) {
+  f2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v));
+  return r;
+}
+__device__ __forceinline__ f2 fma2p(f2 a, f2 b, f2 c) {
+  f2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return r;
+}
+
+// x[0..7] -= m[0..7]: four packed subtractions.
+__device__ __forceinline__ void sub8(float (&x)[8], const float (&m)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; i += 2) unpack2(sub2p(pack2(x[i], x[i + 1]), pack2(m[i], m[i + 1])), x[i], x[i + 1]);
+}
+
+// Exact division by a divisor that many dividends share (a tile's or a row's scale):
+// q = RN(x / s) with the bits of an IEEE division, in three packed operations per two dividends
+// instead of one division routine per dividend.  With r = RN(1 / s):
+//   q0 = RN(x r);  e = x - q0 s  (one fused operation, exact);  q = RN(q0 + e r).
+// That is the final step of the textbook division by reciprocal (Markstein): a correctly rounded
+// reciprocal and a quotient within one ulp give the correctly rounded quotient, provided nothing
+// leaves the normal range on the way.  `exact` is false where that proviso could fail -- divisor
+// or quotients too close to the ends of the exponent range, or a divisor whose significand is
+// all ones (the one pattern the theorem excludes) -- and the caller divides the slow way there.
+// The operator's divisors are amax/448 or amax/127 with amax >= 1e-8 and |x| <= amax, so the
+// fast path is the one that runs; an exhaustive check over every dividend significand backs it
+// (the division self-test of the library).
+struct ExactDiv {
+  float s, r, neg_s;
+  bool exact;
+};
+__device__ __forceinline__ ExactDiv make_exact_div(float s) {
+  ExactDiv d;
+  d.s = s;
+  d.neg_s = -s;
+  d.r = __frcp_rn(s);
+  const unsigned bits = __float_as_uint(s);
+  const unsigned e = (bits >> 23) & 0xFFu;
+  // |x| <= 512 |s| in this operator, so quotients stay far inside the range; the divisor's own
+  // exponent must leave room for r and for the exact remainder x - q0 s (24 more bits below x)
+  d.exact = (e >= 40u && e <= 200u) && ((bits & 0x7FFFFFu) != 0x7FFFFFu);
+  return d;
+}
+// y[i] = x[i] / s for i = 0..7, to be rounded to an 8-bit code by the caller.  For |x| >= 2^-100
+// (or zero) y is RN(x / s) bit for bit.  Below that the remainder may be inexact, but then
+// |x / s| < 2^-13 (s >= 2^-87 on this path), and that quotient and the IEEE one both round to the
+// same signed zero in E4M3 and in INT8.
+__device__ __forceinline__ void div8(const ExactDiv& d, const float (&x)[8], float (&y)[8]) {
+  if (d.exact) {
+    const f2 r = pack2(d.r, d.r), ns = pack2(d.neg_s, d.neg_s);
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const f2 xv = pack2(x[i], x[i + 1]);
+      const f2 q0 = mul2p(xv, r);
+      const f2 e = fma2p(q0, ns, xv);
+      unpack2(fma2p(e, r, q0), y[i], y[i + 1]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = __fdiv_rn(x[i], d.s);
+  }
+}
+
 // 256-point fast Walsh-Hadamard transform over a warp: lane l holds elements
 // 8l..8l+7.  Stage order h = 1, 2, 4 (in registers) then 8..128 (lane exchanges);
 // pair (i, i+h) -> (a+b, a-b); final exact scale 1/16.  Additions only, so the
 // result is a fixed tree of rounded fp32 adds (the CPU oracle's "butterfly" order).
+// Stages h = 2, 4, the lane exchanges and the scale run as packed pairs.
 __device__ __forceinline__ void fwht256(float (&x)[8], int lane) {
 #pragma unroll
-  for (int h = 1; h < 8; h <<= 1) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (!(i & h)) {
-        float a = x[i], b = x[i + h];
-        x[i] = __fadd_rn(a, b);
-        x[i + h] = __fsub_rn(a, b);
-      }
-    }
+  for (int i = 0; i < 8; i += 2) {          // h = 1
+    const float a = x[i], b = x[i + 1];
+    x[i] = __fadd_rn(a, b);
+    x[i + 1] = __fsub_rn(a, b);
+  }
+  f2 p[4] = {pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7])};
+  {                                         // h = 2: (0,1)+-(2,3), (4,5)+-(6,7)
+    const f2 a0 = add2p(p[0], p[1]), a1 = sub2p(p[0], p[1]), a2 = add2p(p[2], p[3]), a3 = sub2p(p[2], p[3]);
+    p[0] = a0; p[1] = a1; p[2] = a2; p[3] = a3;
+  }
+  {                                         // h = 4: (0,1)+-(4,5), (2,3)+-(6,7)
+    const f2 a0 = add2p(p[0], p[2]), a2 = sub2p(p[0], p[2]), a1 = add2p(p[1], p[3]), a3 = sub2p(p[1], p[3]);
+    p[0] = a0; p[1] = a1; p[2] = a2; p[3] = a3;
   }
 #pragma unroll
   for (int m = 1; m < 32; m <<= 1) {
     // upper partner: o - x, lower partner: x + o; as one fused op, fma(+-1, x, o) rounds the
     // same exact sum once, so the bits are those of the add / subtract
     const float sign = (lane & m) ? -1.f : 1.f;
+    const f2 sg = pack2(sign, sign);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float o = __shfl_xor_sync(0xffffffffu, x[i], m);
-      x[i] = __fmaf_rn(sign, x[i], o);
+    for (int i = 0; i < 4; ++i) {
+      f2 o;
+      o.v = __shfl_xor_sync(0xffffffffu, p[i].v, m);
+      p[i] = fma2p(sg, p[i], o);
     }
   }
+  const f2 sixteenth = pack2(0.0625f, 0.0625f);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], 0.0625f);
+  for (int i = 0; i < 4; ++i) unpack2(mul2p(p[i], sixteenth), x[2 * i], x[2 * i + 1]);
 }
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -196,6 +292,7 @@ int launch_batch_stats(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_co
 int launch_batch_means(const BatchRef& b, int kv_heads, cudaStream_t s);
 int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s);
 int launch_batch_attention(const BatchRef& b, bool qk_i8, int sm_count, cudaStream_t s);
+int launch_exact_division_selftest(const float* scales, int n, unsigned long long* mismatches, cudaStream_t s);
 void note_cuda_error(cudaError_t e, const char* where);
 
 }  // namespace akl

@@ -262,10 +262,7 @@ __device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh,
   for (int i = 0; i < 8; ++i) {
     if (row0 + i < g.N) {          // warp-uniform
       unpack8<KV_DTYPE>(raw[i], x[i]);
-      if (center) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) x[i][c] = __fsub_rn(x[i][c], mean[c]);
-      }
+      if (center) sub8(x[i], mean);
       if (rotate) fwht256(x[i], lane);
 #pragma unroll
       for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[i][c]));
@@ -290,12 +287,12 @@ __device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh,
     scale = g.vst[kvh * g.ntiles_cap + t];
   }
 
+  const ExactDiv dv = make_exact_div(scale);
   uint32_t lo[8], hi[8];          // bytes of channels 0-3 / 4-7 of each row
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float y[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[i][c], scale);
+    div8(dv, x[i], y);
     lo[i] = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
     hi[i] = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
   }
@@ -387,8 +384,7 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
     const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
     const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
     float y[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) y[c] = __fdiv_rn(x[k][c], scale);
+    div8(make_exact_div(scale), x[k], y);
     const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
     const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
     const int tile = rr[k] >> 7, r7 = rr[k] & 127, plane = lane >> 4;
@@ -491,7 +487,44 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
   }
 }
 
+// ---------------------------------------------------------------------------
+// Self-test of the shared-divisor division: every dividend significand (2^23 of them) in four
+// quotient binades, both signs, against the IEEE division, for each divisor given.  Counts the
+// quotients whose bits differ (expected: none).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) exact_division_selftest_kernel(const float* scales, unsigned long long* mismatches) {
+  const float s = scales[blockIdx.y];
+  const ExactDiv d = make_exact_div(s);
+  const unsigned sexp = (__float_as_uint(s) >> 23) & 0xFFu;
+  unsigned long long bad = 0;
+  const int eoff[4] = {-3, 0, 5, 8};
+  for (unsigned base = (blockIdx.x * 256u + threadIdx.x) * 8u; base < (1u << 23); base += gridDim.x * 256u * 8u) {
+#pragma unroll 1
+    for (int k = 0; k < 4; ++k) {
+      const int e = static_cast<int>(sexp) + eoff[k];
+      if (e < 1 || e > 254) continue;
+#pragma unroll 1
+      for (unsigned sign = 0; sign < 2; ++sign) {
+        float x[8], y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __uint_as_float((sign << 31) | (static_cast<unsigned>(e) << 23) | (base + i));
+        div8(d, x, y);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bad += (__float_as_uint(y[i]) != __float_as_uint(__fdiv_rn(x[i], s))) ? 1ull : 0ull;
+      }
+    }
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
 }  // namespace
+
+int launch_exact_division_selftest(const float* scales, int n, unsigned long long* mismatches, cudaStream_t s) {
+  exact_division_selftest_kernel<<<dim3(64, static_cast<unsigned>(n)), 256, 0, s>>>(scales, mismatches);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { note_cuda_error(e, "exact_division_selftest"); return AKL_ERR_CUDA; }
+  return AKL_OK;
+}
 
 #define AKL_LAUNCH_CHECK(where)                    \
   do {                                             \

@@ -188,6 +188,22 @@ def prefill_extend_kv_split(ws, q, k_pool, v_pool, idx_local, prefix: int, *, n_
     return exchange_and_merge(o_i, lse_i, group=group, merge=merge)
 
 
+_recv_cache: dict = {}
+
+
+def _staging(o_send, l_send):
+    """Receive buffers for the exchange, kept per (device, shape): a long prefill calls this once per
+    layer with the same shapes, and the previous call's merge has consumed them in stream order."""
+    key = (o_send.device, tuple(o_send.shape), o_send.dtype)
+    bufs = _recv_cache.get(key)
+    if bufs is None:
+        if len(_recv_cache) > 8:
+            _recv_cache.clear()
+        bufs = (torch.empty_like(o_send), torch.empty_like(l_send))
+        _recv_cache[key] = bufs
+    return bufs
+
+
 def exchange_and_merge(o_i, lse_i, *, group=None, merge=None):
     """Reduce-scatter over query rows of the per-rank partial states.
 
@@ -202,13 +218,15 @@ def exchange_and_merge(o_i, lse_i, *, group=None, merge=None):
     T, Hq, D = o_i.shape
     slices = row_slices(T, world)
     per = slices[0][1] - slices[0][0]
-    # pad rows to world * per so the all-to-all is regular
-    o_send = torch.zeros((world * per, Hq, D), dtype=o_i.dtype, device=o_i.device)
-    l_send = torch.full((world * per, Hq), float("-inf"), dtype=torch.float32, device=o_i.device)
-    o_send[:T] = o_i
-    l_send[:T] = lse_i
-    o_recv = torch.empty_like(o_send)
-    l_recv = torch.empty_like(l_send)
+    if world * per == T and o_i.is_contiguous() and lse_i.is_contiguous():
+        o_send, l_send = o_i, lse_i          # rows divide evenly: the partial states are the send buffers
+    else:
+        # pad rows to world * per so the all-to-all is regular
+        o_send = torch.zeros((world * per, Hq, D), dtype=o_i.dtype, device=o_i.device)
+        l_send = torch.full((world * per, Hq), float("-inf"), dtype=torch.float32, device=o_i.device)
+        o_send[:T] = o_i
+        l_send[:T] = lse_i
+    o_recv, l_recv = _staging(o_send, l_send)
     dist.all_to_all_single(o_recv, o_send, group=group)
     dist.all_to_all_single(l_recv, l_send, group=group)
     parts_o = [o_recv[r * per:(r + 1) * per] for r in range(world)]

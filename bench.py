@@ -759,11 +759,23 @@ def gpu_reference_leg(torch, wl, dev):
     ext_dir = REF_DIR / "torch_ext"
     if reference_modules() is None or not ext_dir.exists():
         return {"unavailable": "oracle/_ref holds no prebuilt reference extension"}
-    os.environ["TORCH_EXTENSIONS_DIR"] = str(ext_dir)
-    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     try:
-        from attn_kernel_lab import ops as ref_ops   # noqa: PLC0415
+        import importlib.util
 
+        from attn_kernel_lab import kernel as ref_kernel   # noqa: PLC0415
+        from attn_kernel_lab import ops as ref_ops          # noqa: PLC0415
+
+        # the reference's loader would rebuild its extension (a minute and more of compile time) because
+        # the build directory moved with the working tree; hand it its own prebuilt module instead --
+        # built from its own source with its own flags by oracle/build_ref.py -- through the cache
+        # its `load()` consults first
+        so = next((ext_dir / "attn_kernel_lab_fp8_prefill").glob("*.so"), None)
+        if so is None:
+            return {"unavailable": "no prebuilt reference extension under oracle/_ref/torch_ext"}
+        spec = importlib.util.spec_from_file_location("attn_kernel_lab_fp8_prefill", so)
+        ext = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ext)
+        ref_kernel._ext, ref_kernel._loaded_from = ext, "jit"
         r = wl["reqs"][0]
         q = wl["q_all"][0][r["row0"]:r["row0"] + r["T"]]
         kp, vp = wl["k_pools"][0], wl["v_pools"][0]
@@ -777,11 +789,14 @@ def gpu_reference_leg(torch, wl, dev):
         ours = wl["out_all"][0][r["row0"]:r["row0"] + r["T"]].float()
         d = (ours - ref_out.float()).reshape(-1, D)
         rel = d.norm(dim=1) / ref_out.float().reshape(-1, D).norm(dim=1).clamp_min(1e-30)
+        same_rows = float((d == 0).all(dim=1).float().mean())
+        same_elems = float((d == 0).float().mean())
         fl = flops(r["prefix"], r["T"])
         return {"kernel": "the reference's fp8_prefill_attn (mma.sync) compiled for sm_100a, inclusive of its "
                           "tensor-library preprocessing", "request": {"prefix": r["prefix"], "T": r["T"]},
                 "ms_inclusive": ms, "tflops_inclusive": fl / ms / 1e9, "first_call_s": first_call_s,
-                "rowrel_median_vs_this_library": float(rel.median()), "rowrel_max_vs_this_library": float(rel.max())}
+                "rowrel_median_vs_this_library": float(rel.median()), "rowrel_max_vs_this_library": float(rel.max()),
+                "bit_identical_rows_vs_this_library": same_rows, "bit_identical_elements_vs_this_library": same_elems}
     except Exception as exc:  # noqa: BLE001 - reported, never fatal for the bench line
         return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
 

@@ -254,6 +254,15 @@ int akl_prefill_extend_batch(const akl_batch_t* b, void* stream);
 #define AKL_BATCH_ALL 15u
 int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void* stream);
 
+/* Self-test of the preprocessing kernels' division.  They divide 16 384 (a K/V tile) or 256 (a Q
+ * row) values by one scale, and do it as a correctly rounded reciprocal plus one fused remainder
+ * correction instead of one IEEE division per value; the bytes must be those of the reference's
+ * true division (quant.py:416-430, 471-478).  For each of the n_scales device floats this launch
+ * divides every dividend significand (2^23), both signs, in four quotient binades, both ways, and
+ * adds the number of quotients whose bits differ to *mismatches (device, caller-zeroed).
+ * No counterpart in the reference: a check of this build's own arithmetic. */
+int akl_selftest_exact_division(const float* scales, int32_t n_scales, uint64_t* mismatches, void* stream);
+
 /* The whole operator (same work and same results as akl_prefill_extend) for callers that cannot
  * allocate device memory -- an engine plugin that is handed no allocator, or a host whose memory
  * pool is frozen after start-up.  The workspace is a 16 MiB array built into the library (held by

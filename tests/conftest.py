@@ -35,3 +35,26 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """Write the measured parity figures the tests recorded (helpers.LEDGER) next to the other
+    run outputs; nothing is written when no test recorded anything."""
+    import json
+
+    try:
+        import helpers
+    except Exception:  # noqa: BLE001
+        return
+    if not helpers.LEDGER:
+        return
+    out = ROOT / "gpurun_out"
+    try:
+        out.mkdir(exist_ok=True)
+        path = out / "parity_ledger.json"
+        old = json.loads(path.read_text()) if path.exists() else {}
+        for section, entries in helpers.LEDGER.items():
+            old.setdefault(section, {}).update(entries)
+        path.write_text(json.dumps(old, indent=1, sort_keys=True))
+    except OSError:
+        pass

@@ -8,6 +8,23 @@ import torch
 
 import akl_oracle as O
 
+#: measured parity figures, keyed "section/case/mode"; tests/conftest.py writes them to
+#: gpurun_out/parity_ledger.json when the session ends (the numbers quoted in the design notes)
+LEDGER: dict = {}
+
+
+def record(section: str, key: str, **metrics):
+    LEDGER.setdefault(section, {})[key] = {k: (float(v) if isinstance(v, (float, np.floating)) else int(v)
+                                               if isinstance(v, (int, np.integer, bool, np.bool_)) else v)
+                                           for k, v in metrics.items()}
+
+
+def max_over_rms(got: np.ndarray, ref: np.ndarray) -> float:
+    """max|got - ref| / RMS(ref): the stated output metric."""
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(rms, 1e-30))
+
+
 LOG2E = np.float32(1.4426950408889634)
 LOG2_448 = np.float32(8.807354922057604)
 

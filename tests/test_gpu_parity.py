@@ -203,6 +203,9 @@ def test_attention_scores_probabilities_and_output(pkg, cuda, case, qk_i8):
     assert flips_formula <= max(2, 2e-5 * total_p), f"P flips vs exact exp2: {flips_formula}/{total_p}"
     assert H.output_within_bound(got, own).all(), "output vs float64 PV over the kernel's own P"
     assert (got != own).mean() < 5e-3
+    ledger = {"p_flips_vs_exact_exp2": flips_formula, "p_bytes": total_p,
+              "max_over_rms_vs_f64_pv_of_own_p": H.max_over_rms(got, own),
+              "bf16_elements_differing_from_f64_pv": float((got != own).mean())}
 
     # the independent float64 oracle, on the kernel's own quantised bytes (the reference's
     # pattern, tests/kernel/test_ops_gpu.py:48-68)
@@ -220,9 +223,16 @@ def test_attention_scores_probabilities_and_output(pkg, cuda, case, qk_i8):
             flipped[r0:r1, h] |= (mine != p8[r0:r1]).any(axis=1)
     ok = H.output_within_bound(got, ref)
     assert ok[~flipped].all(), "rows whose P bytes equal the oracle's must meet the output bound"
-    assert flipped.mean() <= 0.05, f"{flipped.mean():.3%} of rows carry a P flip"
+    assert flipped.mean() <= 0.02, f"{flipped.mean():.3%} of rows carry a P flip"     # observed: at most 0.9 %
     rel = H.row_rel(got, ref).reshape(T, Hq)
     assert (rel[~flipped] < 9e-3).all() if (~flipped).any() else True
+    assert (rel < 9e-3).mean() >= 0.995, "rows over the reference's own row-relative bound"
+    ledger.update({"rows": int(flipped.size), "rows_with_a_p_flip_vs_oracle": int(flipped.sum()),
+                   "max_over_rms_vs_oracle_all_rows": H.max_over_rms(got, ref),
+                   "max_over_rms_vs_oracle_unflipped_rows": (H.max_over_rms(got[~flipped], ref[~flipped]) if (~flipped).any() else 0.0),
+                   "rows_over_9e-3": int((rel >= 9e-3).sum()), "rowrel_median": float(np.median(rel)),
+                   "rowrel_max": float(rel.max()), "lse_max_abs": float(np.abs(got_lse - ref_lse).max())})
+    H.record("attention_vs_oracle", f"{case['name']}/{'int8' if qk_i8 else 'fp8'}", **ledger)
 
 
 # ------------------------------------------------------------------ the public operator
@@ -262,7 +272,10 @@ def test_against_the_reference_output_fixture(pkg, cuda):
     ref = O.bf16_bits_to_f32(g["out_bf16_bits"])
     got = out.float().cpu().numpy()[:, heads]
     rel = H.row_rel(got, ref)
-    assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.97
+    H.record("public_entry_vs_reference_output_fixture", "c1_cpu_oracle/fp8", rowrel_median=float(np.median(rel)),
+             rowrel_max=float(rel.max()), rows_over_9e_3=int((rel >= 9e-3).sum()), rows=int(rel.size),
+             max_over_rms=H.max_over_rms(got, ref), lse_max_abs=float(np.abs(lse.cpu().numpy()[:, heads] - g["lse"]).max()))
+    assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() >= 0.99
     assert np.abs(lse.cpu().numpy()[:, heads] - g["lse"]).max() < 5e-3
 
 
@@ -499,8 +512,81 @@ def test_main_profile_shape_sampled_oracle_and_properties(pkg, cuda):
     ok = H.output_within_bound(got, ref)
     rel = H.row_rel(got, ref)
     # rows with a flipped P byte are the only ones allowed outside; count them instead of dumping
-    assert ok.reshape(T, len(heads), 256).all(axis=2).mean() > 0.97
-    assert np.median(rel) < 1.5e-3 and (rel < 9e-3).mean() > 0.97
+    inside = ok.reshape(T, len(heads), 256).all(axis=2)
+    H.record("attention_vs_oracle", "main_profile_depth_prefix8192_T2048/fp8", rows=int(inside.size),
+             rows_outside_output_bound=int((~inside).sum()), rows_over_9e_3=int((rel >= 9e-3).sum()),
+             rowrel_median=float(np.median(rel)), rowrel_max=float(rel.max()), max_over_rms=H.max_over_rms(got, ref),
+             lse_max_abs=float(np.abs(lse.cpu().numpy()[:, heads] - ref_lse).max()))
+    assert inside.mean() >= 0.98                      # observed: see the parity ledger
+    assert np.median(rel) < 1.5e-3 and (rel < 9e-3).mean() >= 0.99
+
+
+# ------------------------------------------------------------------ properties ported from the reference's tests
+def test_oracle_comparison_is_sensitive_to_a_three_percent_scale_error(pkg, cuda):
+    """The comparison above must be able to fail: one K tile's scale off by 3 % in the workspace,
+    between the transform and the attention launch, has to break the row-relative bound
+    (the reference's sensitivity check, tests/kernel/test_oracle_a.py:201-219)."""
+    import ctypes
+
+    from attn_kernel_lab_b200 import kernel as K, quant
+
+    case = cases.GOLDEN_CASES[0]
+    inp = cases.make_inputs(case)
+    q, kp, vp, idx = H.to_dev(inp, cuda)
+    ws = pkg.FP8PrefillWorkspace(cuda)
+    out, lse, _ = H.run_phases(pkg, ws, q, kp, vp, idx, case["prefix"], case["sm_scale"])
+    qp, kv = H.workspace_packs(ws, case["T"], case["N"])
+    ref = O.attention(qp, kv, case["prefix"], case["T"], case["H"] // case["KVH"])
+    clean = H.row_rel(out.float().cpu().numpy(), ref)
+    assert (clean < 9e-3).mean() >= 0.995
+    lib = K.load()
+    call = quant.make_call(ws, q=q, k_pool=kp, v_pool=vp, idx=idx, out=out, lse_out=lse, q_len=case["T"],
+                           kv_len=case["N"], prefix=case["prefix"], q_heads=case["H"], kv_heads=case["KVH"],
+                           sm_scale=case["sm_scale"])
+    ws.view("kscale")[:, 1] *= 1.03                 # every kv head, second 64-key tile
+    K.check(lib.akl_attention(ctypes.byref(call), torch.cuda.current_stream().cuda_stream), "akl_attention")
+    torch.cuda.synchronize()
+    broken = H.row_rel(out.float().cpu().numpy(), ref)
+    assert np.median(broken) > 3 * np.median(clean) and (broken >= 9e-3).mean() > 0.2, \
+        "a 3 % scale error went unnoticed: the comparison has no teeth"
+
+
+def test_future_keys_are_invisible(pkg, cuda):
+    """Changing K at the last position (no K centring, so no request-wide statistic of K moves;
+    V untouched) may change only rows that can see that position's 64-key tile: the tile's scale
+    and bytes change, nothing before it does (after tests/kernel/test_divergence_hunting.py:434-460)."""
+    T, N, prefix, Hq, KVH = 200, 1000, 800, 24, 4
+    q = cases.outlier_normal((T, Hq, 256), 4501).to(torch.bfloat16).to(cuda)
+    k = cases.outlier_normal((N, KVH, 256), 4502).to(torch.bfloat16).to(cuda)
+    v = cases.outlier_normal((N, KVH, 256), 4503).to(torch.bfloat16).to(cuda)
+    idx = torch.arange(N, device=cuda)
+    base, base_lse = H.fp8_extend(pkg, q, k, v, idx, prefix, sm_scale=1 / 16, center_k=False, return_lse=True)
+    k2 = k.clone()
+    k2[N - 1] = (k2[N - 1].float() * 3 + 1).to(torch.bfloat16)
+    other, other_lse = H.fp8_extend(pkg, q, k2, v, idx, prefix, sm_scale=1 / 16, center_k=False, return_lse=True)
+    last_tile_start = (N - 1) // 64 * 64                      # rows whose reach ends before this tile are untouched
+    untouched = [r for r in range(T) if prefix + r < last_tile_start]
+    assert len(untouched) > 100
+    assert torch.equal(base[untouched].view(torch.int16), other[untouched].view(torch.int16))
+    assert torch.equal(base_lse[untouched].view(torch.int32), other_lse[untouched].view(torch.int32))
+    assert not torch.equal(base[T - 1], other[T - 1])         # the last row sees the changed key
+
+
+@pytest.mark.parametrize("sm_scale", [1 / 64, 1 / 16, 0.11, 1.0])
+def test_softmax_scale_is_folded_exactly_once(pkg, cuda, sm_scale):
+    """The scale enters only through the Q scales (quant.py:479): the operator at sm_scale must match
+    the float64 oracle at the same sm_scale (after tests/kernel/test_divergence_hunting.py:979-995)."""
+    case = dict(cases.GOLDEN_CASES[2])                        # 100 rows over 200 keys, 16:4
+    inp = cases.make_inputs(case)
+    q, kp, vp, idx = H.to_dev(inp, cuda)
+    out, lse = H.fp8_extend(pkg, q, kp, vp, idx, case["prefix"], sm_scale=sm_scale, return_lse=True)
+    qf, kf, vf = H.gathered(inp)
+    ref, ref_lse = O.reference(qf, kf, vf, case["prefix"], sm_scale=sm_scale, return_lse=True)
+    rel = H.row_rel(out.float().cpu().numpy(), ref)
+    H.record("sm_scale_sweep", f"ragged_100_200/{sm_scale:.4g}", rowrel_median=float(np.median(rel)),
+             rowrel_max=float(rel.max()), rows_over_9e_3=int((rel >= 9e-3).sum()), rows=int(rel.size))
+    assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() >= 0.97
+    assert np.abs(lse.cpu().numpy() - ref_lse).max() < 5e-3
 
 
 # ------------------------------------------------------------------ KV-axis split and merge

@@ -15,6 +15,7 @@ import torch
 
 import akl_oracle as O
 import cases
+import helpers as H
 
 GOLDEN = pathlib.Path(__file__).resolve().parent / "golden"
 SIGMA32 = [0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15,
@@ -166,30 +167,64 @@ def test_int8_qk_oracle_reproduces_the_reference_byte_for_byte(case):
         assert np.abs(lse - g["oracle_a_lse"]).max() < 5e-3
 
 
+def _ulp_mismatch(a, b):
+    """(values whose bits differ, largest difference in units of the last place)."""
+    ia, ib = a.astype(np.float32).view(np.int32).astype(np.int64), b.astype(np.float32).view(np.int32).astype(np.int64)
+    d = np.abs(ia - ib)
+    return int((d != 0).sum()), int(d.max()) if d.size else 0
+
+
+#: what the kernels' reduction order costs against the unmodified reference, per fixture and QK mode:
+#: differing bytes (each one code wide) and scales that differ in the last place.  The kernels' order
+#: is bit-exact against the oracle in that order on the GPU, and the oracle in the reference's order is
+#: bit-exact against the reference, so these counts are the CUDA path against the reference.
+#: (q8, k8, v8 differing bytes; max code step)
+T2_EXPECTED = {}
+
+
+@pytest.mark.parametrize("qk_i8", [False, True], ids=["qk_fp8", "qk_int8"])
 @pytest.mark.parametrize("case", cases.GOLDEN_CASES, ids=lambda c: c["name"])
-def test_cuda_order_twin_against_the_unmodified_reference(case):
+def test_cuda_order_twin_against_the_unmodified_reference(case, qk_i8):
     """The order the CUDA kernels use (butterfly rotation, tiled channel sums) against the
-    reference's artifacts: means within a few ulp, and byte flips rare and one code wide."""
-    g = np.load(GOLDEN / f"{case['name']}.npz")
+    reference's artifacts: means within a few ulp, byte flips rare and one code wide, scales off
+    by at most a few units in the last place.  The counts are recorded, not only bounded."""
+    if qk_i8 and case["name"] not in cases.I8_GOLDEN:
+        pytest.skip("no INT8 fixture for this case")
+    g = np.load(GOLDEN / (f"{case['name']}__i8.npz" if qk_i8 else f"{case['name']}.npz"))
     inp = cases.make_inputs(case)
     rows = inp["idx"]
+    q = inp["q"].float().numpy()
     k = inp["k_pool"][rows].float().numpy()
     v = inp["v_pool"][rows].float().numpy()
-    kv = O.preprocess_kv(k, v, rotation="butterfly" if case["rotate"] else None, center_k=case["center_k"])
-    scale = max(np.abs(g["vmean"]).max(), 1e-3)
-    assert np.abs(kv.vmean - g["vmean"]).max() <= 4e-7 * max(1.0, np.abs(v).max())
-    assert np.abs(kv.kmean - g["kmean"]).max() <= 4e-7 * max(1.0, np.abs(k).max())
-    assert np.allclose(kv.kscale, g["kscale"], rtol=1e-5, atol=0)
-    assert np.allclose(kv.vst, g["vst"], rtol=1e-5, atol=0)
-    if case["store_bytes"]:
-        qp = O.preprocess_q(inp["q"].float().numpy(), case["sm_scale"],
-                            rotation="butterfly" if case["rotate"] else None)
-        for mine, ref in ((qp.q8, g["q8"]), (kv.k8, g["k8"]), (kv.v8, g["v8"])):
-            diff = mine != ref
-            assert diff.mean() <= 2e-3
-            step = np.abs(mine.astype(np.int16) - ref.astype(np.int16))[diff]
-            assert step.size == 0 or step.max() == 1
-    del scale
+    rot_k = "butterfly" if case["rotate"] else None
+    rot_r = "sequential" if case["rotate"] else None
+    mine_q = O.preprocess_q(q, case["sm_scale"], rotation=rot_k, qk_i8=qk_i8)
+    mine = O.preprocess_kv(k, v, rotation=rot_k, center_k=case["center_k"], qk_i8=qk_i8)
+    # the reference's own bytes: the oracle in the reference's order reproduces them (digest-checked above)
+    ref_q = O.preprocess_q(q, case["sm_scale"], rotation=rot_r, qk_i8=qk_i8)
+    ref = O.preprocess_kv(k, v, rotation=rot_r, center_k=case["center_k"], kmean=g["kmean"], vmean=g["vmean"],
+                          qk_i8=qk_i8)
+    assert sha(ref_q.q8) == str(g["sha_q8"]) and sha(ref.k8) == str(g["sha_k8"]) and sha(ref.v8) == str(g["sha_v8"])
+    assert np.abs(mine.vmean - g["vmean"]).max() <= 4e-7 * max(1.0, np.abs(v).max())
+    assert np.abs(mine.kmean - g["kmean"]).max() <= 4e-7 * max(1.0, np.abs(k).max())
+    rec = {}
+    for name, a, b in (("q8", mine_q.q8, ref_q.q8), ("k8", mine.k8, ref.k8), ("v8", mine.v8, ref.v8)):
+        diff = a != b
+        step = np.abs(a.view(np.int8).astype(np.int16) - b.view(np.int8).astype(np.int16))[diff] if qk_i8 and name != "v8" \
+            else np.abs(a.astype(np.int16) - b.astype(np.int16))[diff]
+        rec[f"{name}_flips"], rec[f"{name}_bytes"] = int(diff.sum()), int(diff.size)
+        assert step.size == 0 or step.max() == 1, f"{name}: a flip wider than one code"
+    for name, a, b in (("qscale", mine_q.qscale, g["qscale"]), ("kscale", mine.kscale, g["kscale"]),
+                       ("vst", mine.vst, g["vst"]), ("vscale", mine.vscale, g["vscale"]),
+                       ("kmean", mine.kmean, g["kmean"]), ("vmean", mine.vmean, g["vmean"])):
+        n, worst = _ulp_mismatch(a, b)
+        rec[f"{name}_lastplace"], rec[f"{name}_values"], rec[f"{name}_max_ulp"] = n, int(np.size(a)), worst
+        if name in ("qscale", "kscale", "vst", "vscale"):
+            assert worst <= 20, f"{name}: {worst} ulp"     # observed: at most 10
+    # observed over the fixtures: Q 0, V 0, K at most 5 bytes (1.5e-5 of them)
+    assert rec["q8_flips"] == 0 and rec["v8_flips"] == 0
+    assert rec["k8_flips"] <= max(10, 3e-5 * rec["k8_bytes"])
+    H.record("t2_kernel_order_vs_reference", f"{case['name']}/{'int8' if qk_i8 else 'fp8'}", **rec)
 
 
 # ------------------------------------------------------------------ the reference's own bit-exact matrix
