@@ -223,10 +223,10 @@ def test_attention_scores_probabilities_and_output(pkg, cuda, case, qk_i8):
             flipped[r0:r1, h] |= (mine != p8[r0:r1]).any(axis=1)
     ok = H.output_within_bound(got, ref)
     assert ok[~flipped].all(), "rows whose P bytes equal the oracle's must meet the output bound"
-    assert flipped.mean() <= 0.02, f"{flipped.mean():.3%} of rows carry a P flip"     # observed: at most 0.9 %
+    assert flipped.sum() <= max(2, 0.01 * flipped.size), f"{flipped.mean():.3%} of rows carry a P flip"   # observed: at most 0.4 %
     rel = H.row_rel(got, ref).reshape(T, Hq)
     assert (rel[~flipped] < 9e-3).all() if (~flipped).any() else True
-    assert (rel < 9e-3).mean() >= 0.995, "rows over the reference's own row-relative bound"
+    assert (rel >= 9e-3).sum() <= max(1, 0.002 * rel.size), "rows over the reference's own row-relative bound"   # observed: one row in one case
     ledger.update({"rows": int(flipped.size), "rows_with_a_p_flip_vs_oracle": int(flipped.sum()),
                    "max_over_rms_vs_oracle_all_rows": H.max_over_rms(got, ref),
                    "max_over_rms_vs_oracle_unflipped_rows": (H.max_over_rms(got[~flipped], ref[~flipped]) if (~flipped).any() else 0.0),
