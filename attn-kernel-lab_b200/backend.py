@@ -23,9 +23,15 @@ What differs:
     (default, as in the reference) and "fp8", anything else is treated the same way.
   * requests whose head counts are outside the declared capability surface (for example a
     tensor-parallel shard with 6:1 heads) take the inherited path instead of raising;
-  * the per-request Python loop of three calls (:267-289) is one `prefill_extend_batch` call that
-    writes each request's rows of the output in place; `SGLANG_FP8_PREFILL_STREAMS` (default 1)
-    spreads the requests of a forward over that many streams and workspaces.
+  * the per-request Python loop of three calls (:267-289) is one `prefill_extend_batch` call on the
+    native batched entry (four launches for the whole forward, lengths and page rows in a device
+    table) that writes each request's rows of the output in place; the batch workspace grows when a
+    forward needs more, as the reference's per-backend workspace does;
+  * a query that is not BF16, or a pool that is neither BF16 nor FP16, takes the inherited path
+    before anything is written to the pool (the reference's preprocessing accepts any float type;
+    this operator's contract is BF16 queries).
+  * `register_backend(register)` is the registration the reference's installer appends to SGLang's
+    backend registry (engines/sglang/integration/fp8_prefill/install.py:56-69), as a function.
 
 SGLang is imported only when `FP8PrefillAttnBackend` is first asked for; a harness without SGLang
 builds the class over its own base with `make_backend_class`.
@@ -43,7 +49,9 @@ HEAD_DIM = 256
 
 logger = logging.getLogger(__name__)
 
-__all__ = ["BackendSettings", "ExtendSnapshot", "make_backend_class", "FP8PrefillAttnBackend"]
+__all__ = ["BackendSettings", "ExtendSnapshot", "make_backend_class", "register_backend", "FP8PrefillAttnBackend"]
+
+BACKEND_NAME = "fp8_prefill"
 
 
 @dataclass(frozen=True)
@@ -57,7 +65,6 @@ class BackendSettings:
     qk: str = "int8"
     bf16_heads: str = ""
     debug: bool = False
-    streams: int = 1
 
     @classmethod
     def from_env(cls, env: Optional[Mapping[str, str]] = None) -> "BackendSettings":
@@ -71,7 +78,6 @@ class BackendSettings:
             qk=env.get("SGLANG_FP8_PREFILL_QK", "int8").strip().lower(),
             bf16_heads=env.get("SGLANG_FP8_PREFILL_BF16_HEADS", "").strip(),
             debug=env.get("SGLANG_FP8_PREFILL_DEBUG") == "1",
-            streams=max(1, int(env.get("SGLANG_FP8_PREFILL_STREAMS", "1"))),
         )
 
     def unbuilt_mode(self) -> Optional[str]:
@@ -115,7 +121,7 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
             self._kv_cache_quantized = bool(
                 getattr(model_runner.token_to_kv_pool, "is_quantized_kv_cache", False))
             self._fp8_snapshot: Optional[ExtendSnapshot] = None
-            self._workspaces: list = []
+            self._batch_ws = None
             self._unbuilt = self._settings.unbuilt_mode()
             self._last_decline: Optional[str] = None
             if self._settings.disable:
@@ -123,9 +129,9 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
             elif self._unbuilt:
                 logger.warning("[fp8_prefill] every forward takes the inherited path: %s", self._unbuilt)
             else:
-                logger.info("[fp8_prefill] enabled: qk=%s min_tokens=%d min_extend=%d page_size=%d streams=%d",
+                logger.info("[fp8_prefill] enabled: qk=%s min_tokens=%d min_extend=%d page_size=%d",
                             self._settings.qk, self._settings.min_tokens, self._settings.min_extend,
-                            self._page_size, self._settings.streams)
+                            self._page_size)
 
         # ---- metadata time -------------------------------------------------------------
         def init_forward_metadata(self, forward_batch):
@@ -207,12 +213,29 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
                     logger.info("[fp8_prefill] inherited path: %s", reason)
                 self._last_decline = reason
                 return super().forward_extend(q, k, v, layer, forward_batch, save_kv_cache=save_kv_cache)
-            self._last_decline = None
-
             import torch
 
             from . import ops
-            from .quant import FP8PrefillWorkspace
+            from .quant import FP8PrefillBatchWorkspace
+
+            heads = layer.tp_q_head_num
+            k_pool = self.token_to_kv_pool.get_key_buffer(layer.layer_id)
+            v_pool = self.token_to_kv_pool.get_value_buffer(layer.layer_id)
+            # operand types are checked before the pool write-through: after it the forward could no
+            # longer be handed to the inherited path
+            reason = None
+            if q.dtype != torch.bfloat16:
+                reason = f"query dtype {q.dtype} is not bfloat16"
+            elif k_pool.dtype not in (torch.bfloat16, torch.float16) or v_pool.dtype != k_pool.dtype:
+                reason = f"pool dtype {k_pool.dtype} is neither bfloat16 nor float16"
+            elif not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+                reason = "pool buffers are not contiguous"
+            if reason is not None:
+                if reason != self._last_decline and self._settings.debug:
+                    logger.info("[fp8_prefill] inherited path: %s", reason)
+                self._last_decline = reason
+                return super().forward_extend(q, k, v, layer, forward_batch, save_kv_cache=save_kv_cache)
+            self._last_decline = None
 
             # 1. the chunk's K/V go into the paged pool first; the operator then reads prefix and
             #    chunk alike from the pool
@@ -223,9 +246,6 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
                     getattr(layer, "k_scale", None), getattr(layer, "v_scale", None))
                 self.token_to_kv_pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v, *scales)
 
-            heads = layer.tp_q_head_num
-            k_pool = self.token_to_kv_pool.get_key_buffer(layer.layer_id)
-            v_pool = self.token_to_kv_pool.get_value_buffer(layer.layer_id)
             q3 = q.view(-1, heads, HEAD_DIM)
             out = torch.empty_like(q3)
 
@@ -240,17 +260,41 @@ def make_backend_class(base: type, extend_mode: object, *, name: str = "FP8Prefi
                 requests.append({"q": q3[row0:row0 + e], "k_pool": k_pool, "v_pool": v_pool,
                                  "idx": pages, "prefix": p, "out": out[row0:row0 + e]})
                 row0 += e
-            want = min(self._settings.streams, len(requests))
-            while len(self._workspaces) < want:
-                self._workspaces.append(FP8PrefillWorkspace(q.device))
-            workspace = self._workspaces[0] if want == 1 else self._workspaces[:want]
-            ops.prefill_extend_batch(requests, workspace=workspace, sm_scale=layer.scaling,
+            kv_total = sum(p + e for p, e in zip(snap.prefix_lens, snap.extend_lens))
+            ws = self._batch_ws
+            if (ws is None or ws.device != q.device or (ws.q_heads, ws.kv_heads) != (heads, layer.tp_k_head_num)
+                    or not ws.admits(len(requests), kv_total, q3.shape[0])):
+                # grow with headroom (eager use; a deployment that captures graphs reserves once)
+                ws = FP8PrefillBatchWorkspace(
+                    q.device, max_requests=max(len(requests), 8) * 2, max_total_kv_len=int(kv_total * 1.5) + 1024,
+                    max_total_q_len=int(q3.shape[0] * 1.5) + 256, q_heads=heads, kv_heads=layer.tp_k_head_num)
+                self._batch_ws = ws
+            ops.prefill_extend_batch(requests, workspace=ws, sm_scale=layer.scaling,
                                      qk_i8=self._settings.qk == "int8", rotate=self._settings.rotate,
                                      center_k=self._settings.center_k)
             return out.view(-1, heads * HEAD_DIM)
 
     _Backend.__name__ = _Backend.__qualname__ = name
     return _Backend
+
+
+def register_backend(register, *, name: str = BACKEND_NAME, backend_class: Optional[type] = None):
+    """Register the backend factory under `name` with an attention-backend registry.
+
+    `register` is the registry's decorator factory -- SGLang's `register_attention_backend` -- so that
+    `register(name)(factory)` files the factory.  The factory refuses MLA models and forwards the
+    runner's workspace policy unchanged, as the block the reference's installer appends to SGLang's
+    registry does (engines/sglang/integration/fp8_prefill/install.py:56-69).  `backend_class`
+    defaults to the class bound to the installed SGLang.  Returns the factory."""
+
+    def create_fp8_prefill_backend(runner):
+        if getattr(runner, "use_mla_backend", False):
+            raise ValueError("fp8_prefill does not support MLA models.")
+        cls = backend_class if backend_class is not None else __getattr__("FP8PrefillAttnBackend")
+        return cls(runner, init_new_workspace=runner.init_new_workspace)
+
+    register(name)(create_fp8_prefill_backend)
+    return create_fp8_prefill_backend
 
 
 _sglang_class: Optional[type] = None

@@ -199,8 +199,11 @@ class FP8PrefillWorkspace:
         return self._base[off:off + nbytes].view(dtype).view(shape)
 
     def status(self) -> int:
-        """First device-side error code recorded since allocation (synchronises)."""
+        """First device-side error code recorded since allocation or the last reset (synchronises)."""
         return int(self.view("status")[0].item())
+
+    def reset_status(self) -> None:
+        self.view("status").zero_()
 
     # position-order bytes, as the reference's buffers hold them ---------------------------
     def q8_logical(self, q_len: int) -> torch.Tensor:
@@ -295,8 +298,18 @@ class FP8PrefillBatchWorkspace:
         return self._base.data_ptr()
 
     def status(self) -> int:
-        """First device-side error code recorded since allocation (synchronises)."""
+        """First device-side error code recorded since allocation or the last reset (synchronises)."""
         return int(self._status[0].item())
+
+    def reset_status(self) -> None:
+        self._status.zero_()
+
+    def admits(self, n_requests: int, total_kv_len: int, total_q_len: int) -> bool:
+        """Whether a batch with these totals certainly fits (every request rounds up to whole
+        128-row tiles, so one tile per request is held back)."""
+        return (n_requests <= self.caps.max_requests
+                and _ceil_to(total_kv_len, 128) // 128 + n_requests <= self.caps.max_total_kv_pairs
+                and _ceil_to(total_q_len, MPAD) // MPAD + n_requests <= self.caps.max_total_q_tiles)
 
     # ------------------------------------------------------------------ planning
     def _batch_struct(self, kv_dtype, idx_dtype, flags, sm_scale):

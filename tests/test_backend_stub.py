@@ -15,7 +15,7 @@ def backend_mod(pkg):
 
 def _setup(backend_mod, monkeypatch, *, env=None, prefix=(9000, 8500), extend=(512, 300), page_size=1,
            quantized=False, layer=None):
-    for key in ("DISABLE", "MIN_TOKENS", "MIN_EXTEND", "K_CENTER", "HADAMARD", "QK", "BF16_HEADS", "DEBUG", "STREAMS"):
+    for key in ("DISABLE", "MIN_TOKENS", "MIN_EXTEND", "K_CENTER", "HADAMARD", "QK", "BF16_HEADS", "DEBUG"):
         monkeypatch.delenv("SGLANG_FP8_PREFILL_" + key, raising=False)
     for k, v in (env or {}).items():
         monkeypatch.setenv(k, v)
@@ -60,7 +60,20 @@ def _patch_operator(backend_mod, monkeypatch):
     from attn_kernel_lab_b200 import ops, quant
     rec = Recorder()
     monkeypatch.setattr(ops, "prefill_extend_batch", rec)
-    monkeypatch.setattr(quant, "FP8PrefillWorkspace", lambda device: ("workspace", str(device)))
+    class FakeBatchWorkspace:
+        """Stands in for the batch workspace: records what it was sized for, allocates nothing."""
+        made = []
+
+        def __init__(self, device, *, max_requests, max_total_kv_len, max_total_q_len, q_heads, kv_heads):
+            self.device, self.q_heads, self.kv_heads = device, q_heads, kv_heads
+            self.sizes = (max_requests, max_total_kv_len, max_total_q_len)
+            FakeBatchWorkspace.made.append(self)
+
+        def admits(self, n, kv, qlen):
+            return n <= self.sizes[0] and kv <= self.sizes[1] and qlen <= self.sizes[2]
+
+    monkeypatch.setattr(quant, "FP8PrefillBatchWorkspace", FakeBatchWorkspace)
+    rec.workspace_class = FakeBatchWorkspace
     return rec
 
 
@@ -81,7 +94,12 @@ def test_qualifying_forward_runs_the_operator_from_the_snapshot(backend_mod, mon
     (call,) = rec.calls
     assert call["sm_scale"] == layer.scaling and call["rotate"] and call["center_k"]
     assert call["qk_i8"] is True, "INT8 QK is the default operand type, as in the reference"
-    assert call["workspace"] == ("workspace", "cpu")
+    ws = call["workspace"]
+    assert isinstance(ws, rec.workspace_class) and (ws.q_heads, ws.kv_heads) == (24, 4)
+    assert ws.admits(2, 9512 + 8800, 812), "sized for this forward, with headroom"
+    be.forward_extend(q, k, v, layer, fb, save_kv_cache=False)
+    assert rec.calls[-1]["workspace"] is ws and len(rec.workspace_class.made) == 1, "the workspace is kept between layers"
+    del rec.calls[-1]
     r0, r1 = call["requests"]
     assert r0["prefix"] == 9000 and r1["prefix"] == 8500
     assert torch.equal(r0["idx"], want_rows[0]) and torch.equal(r1["idx"], want_rows[1])
@@ -93,6 +111,44 @@ def test_qualifying_forward_runs_the_operator_from_the_snapshot(backend_mod, mon
     assert (o3[:512] == 1).all() and (o3[512:] == 2).all(), "each request's rows are written in place"
     # the written-through rows are what the pool now holds at out_cache_loc
     assert torch.equal(pool.k[1][fb.out_cache_loc.long()].view(812, -1), k)
+
+
+def test_operand_types_outside_the_contract_decline_before_the_pool_write(backend_mod, monkeypatch):
+    """An FP16-activation model (or an FP32 pool) must take the inherited path, and must do so before
+    the chunk is written through: afterwards the forward could not be handed over any more."""
+    be, fb, layer, (q, k, v), pool, _ = _setup(backend_mod, monkeypatch)
+    rec = _patch_operator(backend_mod, monkeypatch)
+    be.init_forward_metadata(fb)
+    out = be.forward_extend(q.to(torch.float16), k, v, layer, fb)
+    assert rec.calls == [] and pool.writes == [] and be.fallback_calls == [(layer.layer_id, True)]
+    assert (out == -7).all()
+    pool.k[1] = pool.k[1].float()
+    pool.v[1] = pool.v[1].float()
+    be.forward_extend(q, k, v, layer, fb)
+    assert rec.calls == [] and pool.writes == [] and len(be.fallback_calls) == 2
+
+
+def test_register_backend_files_the_factory_under_the_reference_name(backend_mod):
+    registry = {}
+
+    def register_attention_backend(name):          # the shape of SGLang's registry decorator
+        def deco(fn):
+            registry[name] = fn
+            return fn
+        return deco
+
+    class Cls:
+        def __init__(self, runner, **kw):
+            self.runner, self.kw = runner, kw
+
+    factory = backend_mod.register_backend(register_attention_backend, backend_class=Cls)
+    assert registry == {"fp8_prefill": factory}
+    runner = type("Runner", (), {"use_mla_backend": False, "init_new_workspace": "policy"})()
+    made = registry["fp8_prefill"](runner)
+    assert isinstance(made, Cls) and made.runner is runner and made.kw == {"init_new_workspace": "policy"}
+    runner.use_mla_backend = True
+    with pytest.raises(ValueError, match="MLA"):
+        registry["fp8_prefill"](runner)
 
 
 def test_save_kv_cache_false_skips_the_write(backend_mod, monkeypatch):
@@ -146,17 +202,17 @@ def test_other_forward_modes_and_missing_metadata_fall_back(backend_mod, monkeyp
     assert not be._batch_qualifies(fb) and be._layer_supported(layer)
 
 
-def test_knobs_reach_the_operator_and_streams_get_their_own_workspaces(backend_mod, monkeypatch):
+def test_knobs_reach_the_operator(backend_mod, monkeypatch):
     be, fb, layer, (q, k, v), _, _ = _setup(
         backend_mod, monkeypatch, env={"SGLANG_FP8_PREFILL_K_CENTER": "0", "SGLANG_FP8_PREFILL_HADAMARD": "0",
                                        "SGLANG_FP8_PREFILL_QK": "fp8",
-                                       "SGLANG_FP8_PREFILL_STREAMS": "4", "SGLANG_FP8_PREFILL_MIN_TOKENS": "100"})
+                                       "SGLANG_FP8_PREFILL_MIN_TOKENS": "100"})
     rec = _patch_operator(backend_mod, monkeypatch)
     be.init_forward_metadata(fb)
     be.forward_extend(q, k, v, layer, fb)
     (call,) = rec.calls
     assert call["rotate"] is False and call["center_k"] is False and call["qk_i8"] is False
-    assert isinstance(call["workspace"], list) and len(call["workspace"]) == 2    # min(streams, requests)
+    assert isinstance(call["workspace"], rec.workspace_class)
 
 
 def test_row_count_mismatch_is_an_error_not_a_silent_slice(backend_mod, monkeypatch):
