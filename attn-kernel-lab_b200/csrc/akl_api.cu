@@ -232,6 +232,20 @@ int need_q(const akl_call_t* c) { return (c->q == nullptr) ? AKL_ERR_INVALID : A
 int need_out(const akl_call_t* c) { return (c->out == nullptr) ? AKL_ERR_INVALID : AKL_OK; }
 
 }  // namespace
+
+// Every host-side check of the whole-operator entry, with no CUDA call: shared by
+// akl_prefill_extend and the entry that works out of the library's own scratch.
+int validate_prefill_call(const akl_call_t* c, Geom* g) {
+  int rc = build_geom(c, g);
+  if (rc != AKL_OK) return rc;
+  if ((rc = need_q(c)) != AKL_OK) return rc;
+  if ((rc = need_out(c)) != AKL_OK) return rc;
+  if (c->kv_pos0 != 0 || (c->n_total != 0 && c->n_total != c->N) || c->tile0_global != 0)
+    return AKL_ERR_INVALID;   // a split request must make its statistics global between the phases
+  if (c->prefix > c->N - c->T) return AKL_ERR_INVALID;
+  return AKL_OK;
+}
+
 }  // namespace akl
 
 using namespace akl;
@@ -317,13 +331,8 @@ int akl_attention_dump(const akl_call_t* c, float* s_dump, uint8_t* p_dump, void
 
 int akl_prefill_extend(const akl_call_t* c, void* stream) {
   Geom g;
-  int rc = build_geom(c, &g);
+  int rc = validate_prefill_call(c, &g);
   if (rc != AKL_OK) return rc;
-  if ((rc = need_q(c)) != AKL_OK) return rc;
-  if ((rc = need_out(c)) != AKL_OK) return rc;
-  if (c->kv_pos0 != 0 || (c->n_total != 0 && c->n_total != c->N) || c->tile0_global != 0)
-    return AKL_ERR_INVALID;   // a split request must make its statistics global between the phases
-  if (c->prefix > c->N - c->T) return AKL_ERR_INVALID;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if ((rc = launch_kv_tile_stats(g, c->kv_dtype, c->idx_dtype, s, /*with_q=*/true)) != AKL_OK) return rc;
   if ((rc = launch_kv_means(g, s, /*fuse_scales=*/true)) != AKL_OK) return rc;

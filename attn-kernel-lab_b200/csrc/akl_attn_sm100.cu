@@ -671,6 +671,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
             (l > 0.f) ? fmaf(m, kLog2e, log2f(l) - kLog2_448) : -INFINITY;
       }
       tc_fence_before();
+    } else if (grow < g.T) {
+      // a bounded wait ran out (the status word says so): leave no plausible-looking rows behind
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(g.out) + (static_cast<size_t>(grow) * g.Hq + h) * kD;
+      const uint4 nan4 = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+#pragma unroll 1
+      for (int i = 0; i < 16; ++i) *reinterpret_cast<uint4*>(orow + wg * 128 + i * 8) = nan4;
+      if (wg == 0 && g.lse_out != nullptr) g.lse_out[static_cast<size_t>(grow) * g.Hq + h] = INFINITY;
     }
     }   // items
   }

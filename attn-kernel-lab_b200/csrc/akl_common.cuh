@@ -294,5 +294,6 @@ int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int s
 int launch_batch_attention(const BatchRef& b, bool qk_i8, int sm_count, cudaStream_t s);
 int launch_exact_division_selftest(const float* scales, int n, unsigned long long* mismatches, cudaStream_t s);
 void note_cuda_error(cudaError_t e, const char* where);
+int validate_prefill_call(const akl_call_t* c, Geom* g);
 
 }  // namespace akl

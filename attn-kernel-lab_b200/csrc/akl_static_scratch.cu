@@ -16,7 +16,9 @@
 //     outside any stream capture;
 //   * every call uses the same array and overwrites what the previous call left there, so two
 //     calls whose GPU work overlaps (different streams, no dependency) race; serialise them;
-//   * nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+//   * nothing here calls cudaMalloc, cudaFree or any allocating library routine;
+//   * the array's address is looked up once per device and kept: after a cudaDeviceReset the
+//     process must not call this entry point again on that device.
 #include <mutex>
 
 #include "akl_common.cuh"
@@ -30,6 +32,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kScratchWindow +
 
 std::mutex g_mutex;
 unsigned char* g_window[kMaxDevices] = {};   // 1024-byte aligned device address, per device
+unsigned long long g_status_off[kMaxDevices] = {};   // where the last accepted call put its status words
 
 // In host code the array's name is only a handle for the runtime, not a device address: the
 // address a kernel may use comes from cudaGetSymbolAddress, asked with the right device current.
@@ -72,10 +75,40 @@ extern "C" int akl_prefill_extend_static_scratch(const akl_call_t* call, void* s
   }
   unsigned char* window = nullptr;
   if ((rc = static_window(&window)) != AKL_OK) return rc;
+  c.workspace = window;
+  c.workspace_bytes = kScratchWindow;
+  // every host-side refusal comes before anything is enqueued: a refused call leaves the array, and
+  // the status an earlier call recorded there, alone
+  akl::Geom unused;
+  if ((rc = akl::validate_prefill_call(&c, &unused)) != AKL_OK) return rc;
   // the array keeps the previous call's bytes; only the status words must start at zero
   cudaError_t e = cudaMemsetAsync(window + layout.off_status, 0, 256, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) { akl::note_cuda_error(e, "cudaMemsetAsync(status)"); return AKL_ERR_CUDA; }
-  c.workspace = window;
-  c.workspace_bytes = kScratchWindow;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_status_off[dev] = layout.off_status;
+  }
   return akl_prefill_extend(&c, stream);
+}
+
+// Copies the status word of the last accepted static-scratch call on the current device to
+// *host_out, asynchronously on `stream` (read it after synchronising the stream): 0 when clean,
+// AKL_ERR_TIMEOUT when a bounded device-side wait ran out.
+extern "C" int akl_static_scratch_status(int32_t* host_out, void* stream) {
+  if (host_out == nullptr) return AKL_ERR_INVALID;
+  unsigned char* window = nullptr;
+  int rc = static_window(&window);
+  if (rc != AKL_OK) return rc;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return AKL_ERR_CUDA;
+  unsigned long long off;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    off = g_status_off[dev];
+  }
+  e = cudaMemcpyAsync(host_out, window + off, sizeof(int32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) { akl::note_cuda_error(e, "cudaMemcpyAsync(status)"); return AKL_ERR_CUDA; }
+  return AKL_OK;
 }

@@ -37,7 +37,7 @@ EXPORTS = (
     "akl_kv_transform", "akl_quantize_q", "akl_attention", "akl_attention_dump",
     "akl_merge_states", "akl_prefill_extend_static_scratch",
     "akl_batch_layout", "akl_batch_plan", "akl_prefill_extend_batch", "akl_prefill_extend_batch_phases",
-    "akl_selftest_exact_division",
+    "akl_selftest_exact_division", "akl_static_scratch_status",
 )
 
 AKL_OK = 0
@@ -220,6 +220,8 @@ def load():
         lib.akl_prefill_extend_batch_phases.restype = ctypes.c_int
         lib.akl_selftest_exact_division.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
         lib.akl_selftest_exact_division.restype = ctypes.c_int
+        lib.akl_static_scratch_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        lib.akl_static_scratch_status.restype = ctypes.c_int
         _lib = lib
     return _lib
 

@@ -252,14 +252,18 @@ def plan_workspace(device, *, max_kv_len: int, max_q_len: int, q_heads: int | No
 
 def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, lse_out=None,
                    sm_scale=None, qk_i8: bool = True, rotate: bool = True, center_k: bool = True,
-                   return_lse: bool = False, capability: OperatorCapability = V1_CAPABILITY):
+                   return_lse: bool = False, capability: OperatorCapability = V1_CAPABILITY,
+                   check_status: bool = False):
     """Bottom-right-causal paged EXTEND attention over a page-size-1 BF16/FP16 KV pool.
 
     Arguments as in the reference (ops.py:485-553): `q` [q_len, q_heads, 256] BF16; `k_pool`,
     `v_pool` [pool, kv_heads, 256]; `idx` [kv_len] pool rows in position order; `prefix` in
     [0, kv_len - q_len]; query row r attends positions 0 .. prefix + r.  `workspace` from
     `plan_workspace` never reallocates; `out` / `lse_out` are written in place when given.
-    Enqueues on the current CUDA stream and does not synchronise.
+    Enqueues on the current CUDA stream and does not synchronise -- unless `check_status` (not in the
+    reference; a debugging aid) is set: then the call waits for the stream, reads the workspace's
+    status word and raises `NativeError(AKL_ERR_TIMEOUT)` if a bounded device-side wait ran out
+    (the kernel then wrote NaN rows and +inf LSE instead of results).
 
     Returns `out`, or `(out, lse)` with `lse` [q_len, q_heads] FP32 base-2 when `return_lse`."""
     request = check_request(q, k_pool, v_pool, idx, prefix, workspace=workspace, out=out,
@@ -294,7 +298,19 @@ def prefill_extend(q, k_pool, v_pool, idx, prefix, *, workspace=None, out=None, 
     with torch.cuda.device(q.device):
         code = lib.akl_prefill_extend(ctypes.byref(call), torch.cuda.current_stream(q.device).cuda_stream)
     kernel_mod.check(code, "akl_prefill_extend")
+    if check_status:
+        _raise_on_status(ws, kernel_mod, "akl_prefill_extend")
     return (out, lse) if request.return_lse else out
+
+
+def _raise_on_status(ws, kernel_mod, where: str) -> None:
+    import torch
+
+    torch.cuda.current_stream(ws.device).synchronize()
+    code = ws.status()
+    if code != 0:
+        ws.reset_status()
+        kernel_mod.check(code, where + " (device status word)")
 
 
 def plan_batch_workspace(device, *, max_requests: int, max_total_kv_len: int, max_total_q_len: int,
@@ -401,10 +417,33 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Tr
         return _native_batch(requests, workspace, sm_scale=sm_scale, qk_i8=qk_i8, rotate=rotate,
                              center_k=center_k, return_lse=return_lse, capability=capability)
     pool = list(workspace) if isinstance(workspace, (list, tuple)) else [workspace]
-    for i, r in enumerate(requests):
-        check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"],
-                      workspace=pool[i % len(pool)], out=r.get("out"), lse_out=r.get("lse_out"),
-                      sm_scale=sm_scale, return_lse=return_lse, capability=capability)
+    # longest-processing-time-first assignment of requests to workspaces / streams
+    cost = [int(r["q"].shape[0]) * (int(r["prefix"]) + (int(r["q"].shape[0]) + 1) / 2.0)
+            if hasattr(r.get("q"), "shape") and isinstance(r.get("prefix"), int) else 0.0 for r in requests]
+    load = [0.0] * len(pool)
+    lane_of = [0] * len(requests)
+    order = sorted(range(len(requests)), key=lambda i: (-cost[i], i))
+    for i in order:
+        k = min(range(len(pool)), key=lambda j: (load[j], j))
+        lane_of[i] = k
+        load[k] += cost[i]
+    checked = []
+    for i, r in enumerate(requests):       # each request against the workspace it will run on
+        checked.append(check_request(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"],
+                                     workspace=pool[lane_of[i]], out=r.get("out"), lse_out=r.get("lse_out"),
+                                     sm_scale=sm_scale, return_lse=return_lse, capability=capability))
+    if len(pool) > 1 and requests:
+        # outputs the caller did not supply are allocated here, on the current stream, before the
+        # fork: a tensor allocated on a side stream could be handed back to that stream's
+        # allocator pool while the current stream still reads it
+        import torch
+
+        requests = [dict(r) for r in requests]
+        for r, c in zip(requests, checked):
+            if r.get("out") is None:
+                r["out"] = torch.empty_like(r["q"])
+            if c.return_lse and r.get("lse_out") is None:
+                r["lse_out"] = torch.empty((c.q_len, c.q_heads), dtype=torch.float32, device=r["q"].device)
 
     def run(r, ws):
         return prefill_extend(r["q"], r["k_pool"], r["v_pool"], r["idx"], r["prefix"], workspace=ws,
@@ -424,15 +463,6 @@ def prefill_extend_batch(requests, *, workspace, sm_scale=None, qk_i8: bool = Tr
     fork.record(main)
     for side in sides:
         side.wait_event(fork)
-    # longest-processing-time-first assignment of requests to streams
-    cost = [int(r["q"].shape[0]) * (int(r["prefix"]) + (int(r["q"].shape[0]) + 1) / 2.0) for r in requests]
-    load = [0.0] * len(pool)
-    lane_of = [0] * len(requests)
-    order = sorted(range(len(requests)), key=lambda i: (-cost[i], i))
-    for i in order:
-        k = min(range(len(pool)), key=lambda j: (load[j], j))
-        lane_of[i] = k
-        load[k] += cost[i]
     results = [None] * len(requests)
     for i in order:                      # each stream sees its requests longest first
         with torch.cuda.stream(sides[lane_of[i]]):

@@ -275,6 +275,12 @@ int akl_selftest_exact_division(const float* scales, int32_t n_scales, uint64_t*
  * This entry point has no counterpart in the reference. */
 int akl_prefill_extend_static_scratch(const akl_call_t* call, void* stream);
 
+/* The status word of the last accepted static-scratch call on the current device, copied to
+ * *host_out asynchronously on `stream` (synchronise, then read): 0 when clean, AKL_ERR_TIMEOUT when
+ * a bounded device-side wait ran out.  The array's address is cached per device, so neither entry
+ * point may be used on a device after cudaDeviceReset.  No counterpart in the reference. */
+int akl_static_scratch_status(int32_t* host_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

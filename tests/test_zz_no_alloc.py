@@ -70,3 +70,32 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit(pkg, cuda):
     with pytest.raises(K.NativeError, match="does not fit"):
         K.check(code, "akl_prefill_extend_static_scratch")
     assert lib.akl_prefill_extend_static_scratch(None, None) == K.AKL_ERR_INVALID
+
+
+def test_static_scratch_status_is_observable_and_a_refused_call_enqueues_nothing(pkg, cuda):
+    """The status word of this entry point lives inside the library's own array, so the library
+    hands it out itself; and a call refused on the host (here: a prefix out of range) must not
+    clear the status an earlier call left, nor enqueue anything."""
+    from attn_kernel_lab_b200 import kernel as K
+
+    lib = K.load()
+    case = cases.GOLDEN_CASES[0]
+    _run_both(pkg, cuda, case)
+    host = torch.full((1,), 77, dtype=torch.int32).pin_memory()
+    st = torch.cuda.current_stream().cuda_stream
+    K.check(lib.akl_static_scratch_status(host.data_ptr(), st), "akl_static_scratch_status")
+    torch.cuda.synchronize()
+    assert int(host[0]) == 0, "a clean call leaves status 0"
+    assert lib.akl_static_scratch_status(None, st) == K.AKL_ERR_INVALID
+
+    from attn_kernel_lab_b200 import quant
+
+    inp = cases.make_inputs(case)
+    q, kp, vp, idx = (inp[k].to(cuda) for k in ("q", "k_pool", "v_pool", "idx"))
+    holder = quant.FP8PrefillWorkspace(cuda, max_kv_len=64, max_q_len=1, q_heads=case["H"], kv_heads=case["KVH"])
+    out = torch.full_like(q, 3.0)
+    call = quant.make_call(holder, q=q, k_pool=kp, v_pool=vp, idx=idx, out=out, q_len=case["T"], kv_len=case["N"],
+                           prefix=case["N"], q_heads=case["H"], kv_heads=case["KVH"], sm_scale=case["sm_scale"])
+    assert lib.akl_prefill_extend_static_scratch(ctypes.byref(call), st) == K.AKL_ERR_INVALID
+    torch.cuda.synchronize()
+    assert bool((out == 3.0).all()), "nothing ran"
