@@ -137,7 +137,7 @@ struct BatchLayout {
   uint32_t t_geoms, t_stat_off, t_qcta_off, t_items;
 };
 
-constexpr int kQRowsPerCtaHost = 32;   // rows one Q-quantisation CTA covers (8 warps x 4 rows)
+constexpr int kQRowsPerCtaHost = 128;  // rows one Q-quantisation item covers: one 128-row tile of one head
 
 int compute_batch_layout(const akl_batch_caps_t& c, BatchLayout* o) {
   if (c.max_requests < 1 || c.max_total_kv_pairs < 1 || c.max_total_q_tiles < 1 || c.q_heads < 1 || c.kv_heads < 1)

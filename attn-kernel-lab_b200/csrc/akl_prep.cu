@@ -30,10 +30,10 @@ __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta);
 // the tile, but not synchronised: a caller that runs several items per CTA synchronises between them.
 template <int KV_DTYPE, int IDX_DTYPE>
 __device__ __forceinline__ void kv_tile_stats_item(const Geom& g, int item) {
-  __shared__ float sm_k[8][kD];
-  __shared__ float sm_v[8][kD];
-  __shared__ float sm_mx[8][kD];
-  __shared__ float sm_mn[8][kD];
+  __shared__ __align__(16) float sm_k[8][kD];
+  __shared__ __align__(16) float sm_v[8][kD];
+  __shared__ __align__(16) float sm_mx[8][kD];
+  __shared__ __align__(16) float sm_mn[8][kD];
   const int t = item / g.Hkv, kvh = item % g.Hkv;
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
@@ -76,12 +76,17 @@ __device__ __forceinline__ void kv_tile_stats_item(const Geom& g, int item) {
       }
     }
   }
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    sm_k[w][lane * 8 + c] = ks[c];
-    sm_v[w][lane * 8 + c] = vs[c];
-    sm_mx[w][lane * 8 + c] = mx[c];
-    sm_mn[w][lane * 8 + c] = mn[c];
+  // 16-byte stores: a quarter-warp's eight stores cover all 32 banks once (scalar stores of
+  // lane * 8 + c would meet four banks eight deep)
+  {
+    float4* pk = reinterpret_cast<float4*>(&sm_k[w][lane * 8]);
+    float4* pv = reinterpret_cast<float4*>(&sm_v[w][lane * 8]);
+    float4* px = reinterpret_cast<float4*>(&sm_mx[w][lane * 8]);
+    float4* pn = reinterpret_cast<float4*>(&sm_mn[w][lane * 8]);
+    pk[0] = make_float4(ks[0], ks[1], ks[2], ks[3]); pk[1] = make_float4(ks[4], ks[5], ks[6], ks[7]);
+    pv[0] = make_float4(vs[0], vs[1], vs[2], vs[3]); pv[1] = make_float4(vs[4], vs[5], vs[6], vs[7]);
+    px[0] = make_float4(mx[0], mx[1], mx[2], mx[3]); px[1] = make_float4(mx[4], mx[5], mx[6], mx[7]);
+    pn[0] = make_float4(mn[0], mn[1], mn[2], mn[3]); pn[1] = make_float4(mn[4], mn[5], mn[6], mn[7]);
   }
   __syncthreads();
   // the eight 8-row run sums are added in run order
@@ -224,18 +229,14 @@ __global__ void __launch_bounds__(kThreads) kv_scales_kernel(Geom g) {
 //    V: gather, centre, per-tile scale, E4M3, transpose -> swizzled [pair][256][128] image
 //    (quant.py:589-668).  blockIdx.z: 0 = K, 1 = V.
 // ---------------------------------------------------------------------------
-template <int KV_DTYPE, int IDX_DTYPE>
-__device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh, bool is_v) {
-  constexpr int kVRow = 80;                       // padded 64-byte row, keeps 16 B alignment
-  __shared__ float sm_red[8];
-  __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
+// The gather of one (64-row tile, kv head, K or V): this warp's eight rows, 16 bytes per lane each.
+template <int IDX_DTYPE>
+__device__ __forceinline__ void load_tile_rows(const Geom& g, int t, int kvh, bool is_v, uint4 (&raw)[8]) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
   const void* pool = is_v ? g.v_pool : g.k_pool;
-
   long long pr = 0;
   if (lane < 8 && row0 + lane < g.N) pr = load_idx<IDX_DTYPE>(g.idx, row0 + lane);
-  uint4 raw[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     long long p = __shfl_sync(0xffffffffu, pr, i);
@@ -244,6 +245,19 @@ __device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh,
       raw[i] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(pool) + off));
     }
   }
+}
+
+template <int KV_DTYPE>
+__device__ __forceinline__ void transform_tile_rows(const Geom& g, int t, int kvh, bool is_v, const uint4 (&raw)[8]) {
+  // V transpose staging: row d (channel) holds its 64 key bytes as eight 8-byte slots; rows are
+  // 72 bytes apart and slot q of row d sits at position q ^ ((d >> 4) & 7).  A half-warp's stores
+  // (rows 8 apart, one slot each) and its loads (16 consecutive rows, one slot each) then touch
+  // sixteen different 8-byte bank pairs; an unswizzled 80-byte row met two of them sixteen deep.
+  constexpr int kVRow = 72;
+  __shared__ float sm_red[8];
+  __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = t * kTile + w * 8;
   float mean[8];
   {
     const float* mp = (is_v ? g.vmean : g.kmean) + kvh * kD + lane * 8;
@@ -316,17 +330,27 @@ __device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh,
       const uint32_t sel = (c & 3) | ((4 + (c & 3)) << 4);
       const uint32_t b0 = __byte_perm(__byte_perm(src[0], src[1], sel), __byte_perm(src[2], src[3], sel), 0x5410);
       const uint32_t b1 = __byte_perm(__byte_perm(src[4], src[5], sel), __byte_perm(src[6], src[7], sel), 0x5410);
-      *reinterpret_cast<uint2*>(sm_vt + (lane * 8 + c) * kVRow + w * 8) = make_uint2(b0, b1);
+      const int d = lane * 8 + c;
+      *reinterpret_cast<uint2*>(sm_vt + d * kVRow + ((w ^ ((d >> 4) & 7)) * 8)) = make_uint2(b0, b1);
     }
     __syncthreads();
     const int d = threadIdx.x;
     uint8_t* img = g.v8t + (static_cast<size_t>(kvh) * g.npairs_cap + pair) * kImageBytes;
+    const int sw = (d >> 4) & 7;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint4 v = *reinterpret_cast<const uint4*>(sm_vt + d * kVRow + j * 16);
-      *reinterpret_cast<uint4*>(img + swz128(d, half * 64 + j * 16)) = v;
+      const uint2 lo2 = *reinterpret_cast<const uint2*>(sm_vt + d * kVRow + (((2 * j) ^ sw) * 8));
+      const uint2 hi2 = *reinterpret_cast<const uint2*>(sm_vt + d * kVRow + (((2 * j + 1) ^ sw) * 8));
+      *reinterpret_cast<uint4*>(img + swz128(d, half * 64 + j * 16)) = make_uint4(lo2.x, lo2.y, hi2.x, hi2.y);
     }
   }
+}
+
+template <int KV_DTYPE, int IDX_DTYPE>
+__device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh, bool is_v) {
+  uint4 raw[8];
+  load_tile_rows<IDX_DTYPE>(g, t, kvh, is_v, raw);
+  transform_tile_rows<KV_DTYPE>(g, t, kvh, is_v, raw);
 }
 
 template <int KV_DTYPE, int IDX_DTYPE>
@@ -338,59 +362,61 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_kernel(Geom g) {
 // 5. Q: rotate, per-row amax, E4M3, scale*sm_scale  (quant.py:433-480)
 //    one warp per (head, padded row); rows >= T are zero bytes with the clamp scale
 // ---------------------------------------------------------------------------
-constexpr int kQRowsPerWarp = 4;
-constexpr int kQRowsPerCta = 8 * kQRowsPerWarp;
+constexpr int kQRowsPerWarp = 4;                 // rows a warp has in flight
+constexpr int kQPasses = 4;                      // passes per warp
+constexpr int kQRowsPerCta = 8 * kQRowsPerWarp * kQPasses;
+static_assert(kQRowsPerCta == kQTile, "one Q item is one 128-row tile of one head");
 
-// `cta` = index among the Q CTAs; each warp transforms four rows at once (four independent
-// loads, butterflies and divisions in flight).
+// `cta` = head * mtiles + q tile.  Each warp owns 16 consecutive rows of the tile and transforms
+// them four at a time (four independent loads, butterflies and divisions in flight); the loads of
+// the next four rows are issued before the current four are transformed.
 __device__ __forceinline__ void quantize_q_rows(const Geom& g, long long cta) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mpad = g.mtiles * kQTile;
-  const long long item0 = (cta * 8 + w) * kQRowsPerWarp;
-  const long long total = static_cast<long long>(g.Hq) * mpad;
-  float x[kQRowsPerWarp][8];
-  int hh[kQRowsPerWarp], rr[kQRowsPerWarp];
-  uint4 raw[kQRowsPerWarp];
-  // the padded row count is a multiple of 128, so the warp's four consecutive rows share a head:
-  // one 32-bit division per warp instead of two 64-bit ones per row
-  const int head0 = static_cast<int>(static_cast<unsigned>(item0 < total ? item0 : 0) / static_cast<unsigned>(mpad));
-  const int rowin0 = static_cast<int>(static_cast<unsigned>(item0 < total ? item0 : 0) - static_cast<unsigned>(head0) * static_cast<unsigned>(mpad));
+  const int head = static_cast<int>(cta / g.mtiles), tile = static_cast<int>(cta % g.mtiles);
+  if (head >= g.Hq) return;
+  const int row_base = tile * kQTile + w * (kQRowsPerWarp * kQPasses);
+  const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
+  const bool rotate = (g.flags & AKL_FLAG_ROTATE) != 0;
+  const uint16_t* qsrc = reinterpret_cast<const uint16_t*>(g.q) + static_cast<size_t>(head) * kD + lane * 8;
+  uint8_t* img = g.q8 + (static_cast<size_t>(head) * g.mtiles_cap + tile) * kImageBytes + (lane >> 4) * kPlaneBytes;
+  float* qscale = g.qscale + static_cast<size_t>(head) * g.mtiles_cap * kQTile;
+  uint4 raw[kQRowsPerWarp], nxt[kQRowsPerWarp];
+  auto load4 = [&](int pass, uint4 (&dst)[kQRowsPerWarp]) {
 #pragma unroll
-  for (int k = 0; k < kQRowsPerWarp; ++k) {
-    const long long item = item0 + k;
-    hh[k] = head0;
-    rr[k] = rowin0 + k;
-    if (item < total && rr[k] < g.T) {
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(g.q) +
-                            (static_cast<size_t>(rr[k]) * g.Hq + hh[k]) * kD + lane * 8;
-      raw[k] = __ldg(reinterpret_cast<const uint4*>(src));
+    for (int k = 0; k < kQRowsPerWarp; ++k) {
+      const int r = row_base + pass * kQRowsPerWarp + k;
+      if (r < g.T) dst[k] = __ldg(reinterpret_cast<const uint4*>(qsrc + static_cast<size_t>(r) * g.Hq * kD));
     }
-  }
+  };
+  load4(0, raw);
 #pragma unroll
-  for (int k = 0; k < kQRowsPerWarp; ++k) {
-    const long long item = item0 + k;
-    if (item >= total) continue;                       // warp-uniform
-    float amax = 0.f;
-    if (rr[k] < g.T) {
-      unpack8<AKL_KV_BF16>(raw[k], x[k]);
-      if (g.flags & AKL_FLAG_ROTATE) fwht256(x[k], lane);
+  for (int pass = 0; pass < kQPasses; ++pass) {
+    if (pass + 1 < kQPasses) load4(pass + 1, nxt);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[k][c]));
-    } else {
+    for (int k = 0; k < kQRowsPerWarp; ++k) {
+      const int r = row_base + pass * kQRowsPerWarp + k;
+      float x[8];
+      float amax = 0.f;
+      if (r < g.T) {
+        unpack8<AKL_KV_BF16>(raw[k], x);
+        if (rotate) fwht256(x, lane);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) x[k][c] = 0.f;
+        for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[c]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) x[c] = 0.f;
+      }
+      amax = fmaxf(warp_max(amax), 1e-8f);
+      const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
+      float y[8];
+      div8(make_exact_div(scale), x, y);
+      const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
+      const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
+      *reinterpret_cast<uint2*>(img + swz128(r & 127, (lane & 15) * 8)) = make_uint2(lo, hi);
+      if (lane == 0) qscale[r] = __fmul_rn(scale, g.sm_scale);
     }
-    amax = fmaxf(warp_max(amax), 1e-8f);
-    const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
-    const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
-    float y[8];
-    div8(make_exact_div(scale), x[k], y);
-    const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
-    const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
-    const int tile = rr[k] >> 7, r7 = rr[k] & 127, plane = lane >> 4;
-    uint8_t* img = g.q8 + (static_cast<size_t>(hh[k]) * g.mtiles_cap + tile) * kImageBytes;
-    *reinterpret_cast<uint2*>(img + plane * kPlaneBytes + swz128(r7, (lane & 15) * 8)) = make_uint2(lo, hi);
-    if (lane == 0) g.qscale[static_cast<size_t>(hh[k]) * g.mtiles_cap * kQTile + rr[k]] = __fmul_rn(scale, g.sm_scale);
+#pragma unroll
+    for (int k = 0; k < kQRowsPerWarp; ++k) raw[k] = nxt[k];
   }
 }
 
@@ -432,12 +458,7 @@ __device__ __noinline__ void stats_or_q_item(const Geom& g, int in_req, bool is_
 }
 
 template <int KV_DTYPE, int IDX_DTYPE>
-__device__ __noinline__ void transform_item_call(const Geom& g, int in_req, bool is_v) {
-  kv_transform_item<KV_DTYPE, IDX_DTYPE>(g, in_req / g.Hkv, in_req % g.Hkv, is_v);
-}
-
-template <int KV_DTYPE, int IDX_DTYPE>
-__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_batch_kernel(BatchRef b) {
+__global__ void __launch_bounds__(kThreads, 3) kv_tile_stats_batch_kernel(BatchRef b) {
   __shared__ Geom sg;
   const BatchHeader* hdr = batch_header(b);
   const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = n_stat + hdr->n_q_ctas;
@@ -469,6 +490,56 @@ __global__ void __launch_bounds__(kMeansThreads) kv_means_batch_kernel(BatchRef 
   kv_means_head<true>(sg, kvh);
 }
 
+#ifdef AKL_XF_PREFETCH
+// The rows of the CTA's next item are requested before the current item is transformed, so the
+// gather's latency runs under the arithmetic (the transform is bound by instruction issue, the
+// gather by latency; side by side they hide each other).  Only when the next item belongs to
+// another request is its gather issued after the geometry has been swapped.
+template <int KV_DTYPE, int IDX_DTYPE>
+__global__ void __launch_bounds__(kThreads, 2) kv_transform_batch_kernel(BatchRef b) {
+  __shared__ Geom sg;
+  const BatchHeader* hdr = batch_header(b);
+  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = 2 * n_stat;
+  const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
+  int cur = -1;
+  int item = blockIdx.x;
+  if (item >= n_all) return;
+  uint4 raw[8], nxt[8];
+  bool is_v = item >= n_stat;
+  int local = is_v ? item - n_stat : item;
+  int r = find_request(stat_off, n_req, local);
+  stage_geom(b, r, cur, &sg);
+  int in_req = local - __ldg(stat_off + r);
+  load_tile_rows<IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
+  while (true) {
+    const int next = item + static_cast<int>(gridDim.x);
+    bool n_is_v = false, prefetched = false;
+    int n_in_req = 0, n_r = -1;
+    if (next < n_all) {
+      n_is_v = next >= n_stat;
+      const int n_local = n_is_v ? next - n_stat : next;
+      n_r = find_request(stat_off, n_req, n_local);
+      n_in_req = n_local - __ldg(stat_off + n_r);
+      if (n_r == cur) {
+        load_tile_rows<IDX_DTYPE>(sg, n_in_req / sg.Hkv, n_in_req % sg.Hkv, n_is_v, nxt);
+        prefetched = true;
+      }
+    }
+    transform_tile_rows<KV_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
+    __syncthreads();                                   // the item's shared-memory staging is dead
+    if (next >= n_all) break;
+    item = next; is_v = n_is_v; in_req = n_in_req;
+    if (prefetched) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) raw[i] = nxt[i];
+    } else {
+      stage_geom(b, n_r, cur, &sg);
+      load_tile_rows<IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
+    }
+  }
+}
+
+#else
 template <int KV_DTYPE, int IDX_DTYPE>
 __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRef b) {
   __shared__ Geom sg;
@@ -482,10 +553,11 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
     const int r = find_request(stat_off, n_req, local);
     stage_geom(b, r, cur, &sg);
     const int in_req = local - __ldg(stat_off + r);
-    transform_item_call<KV_DTYPE, IDX_DTYPE>(sg, in_req, is_v);
+    kv_transform_item<KV_DTYPE, IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v);
     __syncthreads();
   }
 }
+#endif
 
 // ---------------------------------------------------------------------------
 // Self-test of the shared-divisor division: every dividend significand (2^23 of them) in four
@@ -535,10 +607,7 @@ int launch_exact_division_selftest(const float* scales, int n, unsigned long lon
     }                                              \
   } while (0)
 
-static unsigned q_ctas(const Geom& g) {
-  const long long items = static_cast<long long>(g.Hq) * g.mtiles * kQTile;
-  return static_cast<unsigned>((items + kQRowsPerCta - 1) / kQRowsPerCta);
-}
+static unsigned q_ctas(const Geom& g) { return static_cast<unsigned>(g.Hq) * static_cast<unsigned>(g.mtiles); }
 
 template <bool kWithQ>
 static void launch_stats_impl(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t s) {
@@ -592,7 +661,7 @@ int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t
 }
 
 int launch_batch_stats(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
-  const unsigned grid = static_cast<unsigned>(sm_count) * 4u;        // four resident CTAs per SM
+  const unsigned grid = static_cast<unsigned>(sm_count) * 3u;        // three resident CTAs per SM
   if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
     kv_tile_stats_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
   else if (kv_dtype == AKL_KV_BF16)
@@ -612,7 +681,11 @@ int launch_batch_means(const BatchRef& b, int kv_heads, cudaStream_t s) {
 }
 
 int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
+#ifdef AKL_XF_PREFETCH
+  const unsigned grid = static_cast<unsigned>(sm_count) * 2u;        // two resident CTAs per SM
+#else
   const unsigned grid = static_cast<unsigned>(sm_count) * 3u;        // three resident CTAs per SM
+#endif
   if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
     kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
   else if (kv_dtype == AKL_KV_BF16)

@@ -82,11 +82,11 @@ def test_plan_writes_header_totals_and_a_longest_first_work_list(K):
     hdr = table[:64].view(np.int32)
     nt = [(n + 63) // 64 for _, n, _ in shapes]
     mt = [(t + 127) // 128 for t, _, _ in shapes]
-    assert hdr[1] == 3 and hdr[2] == sum(nt) * 4 and hdr[3] == sum(mt) * 24 * 4 and hdr[4] == sum(mt) * 24
+    assert hdr[1] == 3 and hdr[2] == sum(nt) * 4 and hdr[3] == sum(mt) * 24 and hdr[4] == sum(mt) * 24
     stat = table[lay.table_off_stat_totals:lay.table_off_stat_totals + 5 * 4].view(np.int32)
     assert stat.tolist() == [0, nt[0] * 4, (nt[0] + nt[1]) * 4, sum(nt) * 4, sum(nt) * 4]
     qcta = table[lay.table_off_qcta_totals:lay.table_off_qcta_totals + 5 * 4].view(np.int32)
-    assert qcta.tolist() == [0, mt[0] * 96, (mt[0] + mt[1]) * 96, sum(mt) * 96, sum(mt) * 96]
+    assert qcta.tolist() == [0, mt[0] * 24, (mt[0] + mt[1]) * 24, sum(mt) * 24, sum(mt) * 24]
     items = table[lay.table_off_items:lay.table_off_items + hdr[4] * 8].view(np.int32).reshape(-1, 2)
     # requests in order of attended pairs (2, 0, 1); inside a request deepest q tile first, heads together
     assert items[:, 0].tolist() == [2] * 48 + [0] * 48 + [1] * 24
