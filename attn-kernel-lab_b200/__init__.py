@@ -9,6 +9,7 @@ from .backend import BackendSettings, make_backend_class
 from .capability import (
     CapabilityError,
     GENERALIZATION_CAPABILITY,
+    KV_HEAD_SHARD_CAPABILITY,
     OperatorCapability,
     V1_CAPABILITY,
     check_supported,
@@ -21,7 +22,7 @@ from .quant import (BatchPlan, CapacityPlan, FP8PrefillBatchWorkspace, FP8Prefil
                     WorkspaceCapacityError)
 
 __all__ = [
-    "CapabilityError", "GENERALIZATION_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
+    "CapabilityError", "GENERALIZATION_CAPABILITY", "KV_HEAD_SHARD_CAPABILITY", "OperatorCapability", "V1_CAPABILITY",
     "check_supported", "NativeError", "build", "load", "source_build_id", "PrefillRequest",
     "check_request", "plan_workspace", "plan_batch_workspace", "prefill_extend", "prefill_extend_batch",
     "CapacityPlan", "BatchPlan", "FP8PrefillBatchWorkspace",

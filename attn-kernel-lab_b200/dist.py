@@ -59,6 +59,41 @@ def kv_head_slice(q_heads: int, kv_heads: int, part: int, parts: int):
     return (part * per * g, (part + 1) * per * g), (part * per, (part + 1) * per)
 
 
+def prefill_extend_kv_head_shard(q, k_pool, v_pool, idx, prefix, *, part: int, parts: int, out=None, lse_out=None,
+                                 workspace=None, pool_is_sharded: bool = False, **kwargs):
+    """One KV-head-group shard of a request: the part of the work rank `part` of `parts` owns.
+
+    `q` is the request's full query tensor [T, Hq, 256]; the shard attends its q heads
+    `kv_head_slice(...)[0]` to its kv heads.  `k_pool` / `v_pool` are either the full pools
+    [pool, Hkv, 256] (the shard's heads are taken out of them) or, with `pool_is_sharded`, this rank's
+    own [pool, Hkv / parts, 256] slice, as a tensor-parallel engine keeps it.  `out` / `lse_out`, when
+    given, are the FULL [T, Hq, 256] / [T, Hq] tensors and only this shard's heads are written.
+    Returns (out_shard [T, Hq/parts, 256], lse_shard or None, (q_head_lo, q_head_hi)).
+
+    No collective: query heads read one kv head, and every statistic is per kv head, so the shard's
+    rows are bit-identical to the same heads of the unsharded call."""
+    from . import ops
+    from .capability import KV_HEAD_SHARD_CAPABILITY
+
+    Hq = int(q.shape[1])
+    Hkv_total = int(k_pool.shape[1]) * (parts if pool_is_sharded else 1)
+    (qlo, qhi), (klo, khi) = kv_head_slice(Hq, Hkv_total, part, parts)
+    q_s = q[:, qlo:qhi].contiguous()
+    if pool_is_sharded:
+        kp, vp = k_pool, v_pool
+    else:
+        kp, vp = k_pool[:, klo:khi].contiguous(), v_pool[:, klo:khi].contiguous()
+    want_lse = bool(kwargs.pop("return_lse", lse_out is not None))
+    res = ops.prefill_extend(q_s, kp, vp, idx, prefix, workspace=workspace, return_lse=want_lse,
+                             capability=KV_HEAD_SHARD_CAPABILITY, **kwargs)
+    o_s, l_s = res if want_lse else (res, None)
+    if out is not None:
+        out[:, qlo:qhi].copy_(o_s)
+    if lse_out is not None:
+        lse_out[:, qlo:qhi].copy_(l_s)
+    return o_s, l_s, (qlo, qhi)
+
+
 def kv_split_ranges(n_total: int, world: int, granule: int = SPLIT_GRANULE):
     """Cut [0, n_total) into `world` contiguous ranges whose interior boundaries are
     multiples of `granule`.  Trailing ranks may be empty when n_total is small."""

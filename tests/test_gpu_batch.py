@@ -173,3 +173,34 @@ def test_serving_shaped_batch_native_entry_equals_the_stream_batch(pkg, cuda):
     ref_o, _ = H.oracle_row_block(reqs[i]["q"].cpu(), kp[rows].cpu(), vp[rows].cpu(), p, 1 / 16, 5, 0, max(0, t - 32), t)
     rel = H.row_rel(got[i][max(0, t - 32):t, 5].float().cpu().numpy(), ref_o)
     assert np.median(rel) < 2e-3 and (rel < 9e-3).mean() > 0.95
+
+
+@pytest.mark.parametrize("hq, parts", [(24, 4), (32, 2), (16, 4)])
+def test_kv_head_group_shards_concatenate_to_the_unsharded_result(pkg, cuda, hq, parts):
+    """Partition by KV-head group (no exchange): every shard runs the operator on its own heads only --
+    on the full pools or on a tensor-parallel slice of them -- and the shards' rows are bit-identical
+    to those heads of the unsharded call, output and LSE alike."""
+    from attn_kernel_lab_b200 import dist as D
+
+    T, N, prefix, KVH = 200, 1500, 1300, 4
+    q = cases.outlier_normal((T, hq, 256), 4601).to(torch.bfloat16).to(cuda)
+    kp = cases.outlier_normal((N + 50, KVH, 256), 4602).to(torch.bfloat16).to(cuda)
+    vp = cases.outlier_normal((N + 50, KVH, 256), 4603).to(torch.bfloat16).to(cuda)
+    idx = torch.randperm(N + 50, generator=torch.Generator().manual_seed(4604))[:N].to(cuda)
+    whole, whole_lse = H.fp8_extend(pkg, q, kp, vp, idx, prefix, sm_scale=1 / 16, return_lse=True)
+    out = torch.full_like(q, float("nan"))
+    lse = torch.full((T, hq), float("nan"), dtype=torch.float32, device=cuda)
+    covered = []
+    for part in range(parts):
+        sharded = part % 2 == 1                       # alternate: full pools / this rank's slice of the pools
+        (_, _), (klo, khi) = D.kv_head_slice(hq, KVH, part, parts)
+        kps, vps = (kp[:, klo:khi].contiguous(), vp[:, klo:khi].contiguous()) if sharded else (kp, vp)
+        o_s, l_s, (qlo, qhi) = D.prefill_extend_kv_head_shard(
+            q, kps, vps, idx, prefix, part=part, parts=parts, out=out, lse_out=lse, pool_is_sharded=sharded,
+            sm_scale=1 / 16, qk_i8=False)
+        covered.append((qlo, qhi))
+        assert o_s.shape == (T, hq // parts, 256)
+    assert covered == [(i * hq // parts, (i + 1) * hq // parts) for i in range(parts)]
+    assert torch.equal(bits(out), bits(whole)) and torch.equal(bits(lse), bits(whole_lse))
+    with pytest.raises(pkg.CapabilityError):          # a shard shape is not on the production surface
+        pkg.prefill_extend(q[:, :6].contiguous(), kp[:, :1].contiguous(), vp[:, :1].contiguous(), idx, prefix)
