@@ -282,12 +282,18 @@ def phase_rooflines(torch, K, stepper, wl, peaks, fp8_peak):
     attn_flops = sum(flops(r["prefix"], r["T"]) for r in reqs)
     achieved = attn_flops / ms["attention"] / 1e9
     peak = fp8_peak if fp8_peak else 2.0 * peaks["bf16_tflops"]
-    traffic = None
+    traffic = traffic_note = None
     tpath = ROOT / "profiles" / "attn_sm100_traffic.json"
     if tpath.exists():
-        traffic = json.loads(tpath.read_text()).get("dram_bytes_per_launch")
+        cap = json.loads(tpath.read_text())
+        # the capture covers two requests (a full-size launch is too large to profile); DRAM traffic
+        # follows the units processed (Q8 + K8 + V8 + output bytes), so scale it to this launch
+        units = sum(r["T"] * HQ * D + 2 * r["N"] * HKV * D + r["T"] * HQ * D * 2 for r in reqs)
+        traffic = cap["dram_bytes_per_launch"] * units / cap["captured_units_bytes"]
+        traffic_note = (f"ncu capture of a 2-request launch ({cap['dram_bytes_per_launch']} B) scaled by the "
+                        f"units processed ({units} / {cap['captured_units_bytes']} B)")
     roof = {"bound": "tensor", "kernel": "attn_sm100_kernel (persistent, one launch per 8-request layer)",
-            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic,
+            "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_note,
             "peak_source": ("measured FP8 E4M3 GEMM 8192^3 in this run (tensor library, burst)" if fp8_peak
                             else "2 x measured BF16 burst peak (MEASURED_PEAKS.json)"),
             "frac_of_2x_measured_bf16_burst": achieved / (2.0 * peaks["bf16_tflops"]),
