@@ -517,8 +517,8 @@ def test_main_profile_shape_sampled_oracle_and_properties(pkg, cuda):
              rows_outside_output_bound=int((~inside).sum()), rows_over_9e_3=int((rel >= 9e-3).sum()),
              rowrel_median=float(np.median(rel)), rowrel_max=float(rel.max()), max_over_rms=H.max_over_rms(got, ref),
              lse_max_abs=float(np.abs(lse.cpu().numpy()[:, heads] - ref_lse).max()))
-    assert inside.mean() >= 0.98                      # observed: see the parity ledger
-    assert np.median(rel) < 1.5e-3 and (rel < 9e-3).mean() >= 0.99
+    assert inside.mean() >= 0.995                     # observed: every row inside
+    assert np.median(rel) < 1.5e-3 and (rel < 9e-3).mean() >= 0.998      # observed: none over, max 4.6e-3
 
 
 # ------------------------------------------------------------------ properties ported from the reference's tests
