@@ -267,6 +267,67 @@ __device__ __forceinline__ void fwht256(float (&x)[8], int lane) {
   for (int i = 0; i < 4; ++i) unpack2(mul2p(p[i], sixteenth), x[2 * i], x[2 * i + 1]);
 }
 
+// The same transform with a row spread over FOUR lanes: lane q (= lane & 3) holds the channels
+// 32k + 8q + c, k = 0..7, c = 0..7, as x[k][c].  Stages h = 1, 2, 4 run inside x[k][.], h = 8, 16
+// are the only lane exchanges (partners lane ^ 1, lane ^ 2), h = 32, 64, 128 run across k in
+// registers: 128 shuffles per 64 elements instead of 320, and the same pairs, the same order of
+// stages, the same rounded additions - so the same bits.
+__device__ __forceinline__ void fwht256_quarter(float (&x)[8][8], int lane) {
+  f2 p[8][4];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {          // h = 1
+      const float a = x[k][i], b = x[k][i + 1];
+      x[k][i] = __fadd_rn(a, b);
+      x[k][i + 1] = __fsub_rn(a, b);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[k][i] = pack2(x[k][2 * i], x[k][2 * i + 1]);
+    {                                         // h = 2
+      const f2 a0 = add2p(p[k][0], p[k][1]), a1 = sub2p(p[k][0], p[k][1]), a2 = add2p(p[k][2], p[k][3]), a3 = sub2p(p[k][2], p[k][3]);
+      p[k][0] = a0; p[k][1] = a1; p[k][2] = a2; p[k][3] = a3;
+    }
+    {                                         // h = 4
+      const f2 a0 = add2p(p[k][0], p[k][2]), a2 = sub2p(p[k][0], p[k][2]), a1 = add2p(p[k][1], p[k][3]), a3 = sub2p(p[k][1], p[k][3]);
+      p[k][0] = a0; p[k][1] = a1; p[k][2] = a2; p[k][3] = a3;
+    }
+  }
+#pragma unroll
+  for (int m = 1; m < 4; m <<= 1) {           // h = 8, 16: upper partner o - x, lower partner x + o
+    const float sign = (lane & m) ? -1.f : 1.f;
+    const f2 sg = pack2(sign, sign);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        f2 o;
+        o.v = __shfl_xor_sync(0xffffffffu, p[k][i].v, m);
+        p[k][i] = fma2p(sg, p[k][i], o);
+      }
+    }
+  }
+#pragma unroll
+  for (int hk = 1; hk < 8; hk <<= 1) {        // h = 32, 64, 128: pairs (k, k + hk)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k & hk) continue;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const f2 a = p[k][i], b = p[k + hk][i];
+        p[k][i] = add2p(a, b);
+        p[k + hk][i] = sub2p(a, b);
+      }
+    }
+  }
+  const f2 sixteenth = pack2(0.0625f, 0.0625f);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) unpack2(mul2p(p[k][i], sixteenth), x[k][2 * i], x[k][2 * i + 1]);
+  }
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));

@@ -10,7 +10,10 @@
 //   CTA  = one 64-row tile of one kv head, 256 threads;
 //   warp = 8 consecutive rows of the tile;
 //   lane = 8 consecutive channels (one 16-byte load per row).
+#include <atomic>
+
 #include "akl_common.cuh"
+#include "akl_sm100_ptx.cuh"
 
 namespace akl {
 
@@ -247,20 +250,25 @@ __device__ __forceinline__ void load_tile_rows(const Geom& g, int t, int kvh, bo
   }
 }
 
+// V transpose staging: row d (channel) holds its 64 key bytes as eight 8-byte slots; rows are
+// 72 bytes apart and slot q of row d sits at position q ^ ((d >> 4) & 7).  A half-warp's stores
+// (rows 8 apart, one slot each) and its loads (16 consecutive rows, one slot each) then touch
+// sixteen different 8-byte bank pairs; an unswizzled 80-byte row met two of them sixteen deep.
+constexpr int kVRow = 72;
+constexpr int kVStagingBytes = kD * kVRow;
+
+// `sm_vt`: kVStagingBytes of shared memory, 16-byte aligned, that no thread still reads for
+// anything else (the V path writes it without a barrier of its own).  `mp`: this lane's eight
+// channel means (global or shared memory, 16-byte aligned).  `v_scale`: the tile's V scale
+// (ignored for K, whose scale is formed here).
 template <int KV_DTYPE>
-__device__ __forceinline__ void transform_tile_rows(const Geom& g, int t, int kvh, bool is_v, const uint4 (&raw)[8]) {
-  // V transpose staging: row d (channel) holds its 64 key bytes as eight 8-byte slots; rows are
-  // 72 bytes apart and slot q of row d sits at position q ^ ((d >> 4) & 7).  A half-warp's stores
-  // (rows 8 apart, one slot each) and its loads (16 consecutive rows, one slot each) then touch
-  // sixteen different 8-byte bank pairs; an unswizzled 80-byte row met two of them sixteen deep.
-  constexpr int kVRow = 72;
+__device__ __forceinline__ void transform_tile_rows(const Geom& g, int t, int kvh, bool is_v, const uint4 (&raw)[8], uint8_t* sm_vt,
+                                                    const float* mp, float v_scale) {
   __shared__ float sm_red[8];
-  __shared__ __align__(16) uint8_t sm_vt[kD * kVRow];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = t * kTile + w * 8;
   float mean[8];
   {
-    const float* mp = (is_v ? g.vmean : g.kmean) + kvh * kD + lane * 8;
     const float4 m0 = *reinterpret_cast<const float4*>(mp);
     const float4 m1 = *reinterpret_cast<const float4*>(mp + 4);
     mean[0] = m0.x; mean[1] = m0.y; mean[2] = m0.z; mean[3] = m0.w;
@@ -298,7 +306,7 @@ __device__ __forceinline__ void transform_tile_rows(const Geom& g, int t, int kv
     scale = __fdiv_rn(a, qk_i8 ? kInt8Max : kFp8Max);
     if (threadIdx.x == 0) g.kscale[kvh * g.ntiles_cap + t] = scale;
   } else {
-    scale = g.vst[kvh * g.ntiles_cap + t];
+    scale = v_scale;
   }
 
   const ExactDiv dv = make_exact_div(scale);
@@ -346,11 +354,74 @@ __device__ __forceinline__ void transform_tile_rows(const Geom& g, int t, int kv
   }
 }
 
+// K out of a row stage in shared memory, a row spread over four lanes (fwht256_quarter): warp w
+// transforms rows 8w .. 8w+7 of the tile, lane = 4 * (row in the warp) + quarter.  `rows`: the 64
+// rows of 512 bytes; `mean`: the kv head's 256 channel means (shared memory).  Same bytes as the
+// K path of transform_tile_rows.
+template <int KV_DTYPE>
+__device__ __forceinline__ void transform_k_tile_staged(const Geom& g, int t, int kvh, const uint8_t* rows, const float* mean) {
+  __shared__ float sm_redk[8];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane & 3, lr = w * 8 + (lane >> 2);          // row inside the tile
+  const bool live = t * kTile + lr < g.N;
+  const bool center = (g.flags & AKL_FLAG_CENTER_K) != 0;
+  const bool rotate = (g.flags & AKL_FLAG_ROTATE) != 0;
+  const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
+  float x[8][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (live) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(rows + lr * (kD * 2) + k * 64 + q * 16);
+      unpack8<KV_DTYPE>(raw, x[k]);
+      if (center) {
+        const float4 m0 = *reinterpret_cast<const float4*>(mean + k * 32 + q * 8);
+        const float4 m1 = *reinterpret_cast<const float4*>(mean + k * 32 + q * 8 + 4);
+        const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        sub8(x[k], m);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) x[k][c] = 0.f;             // padding rows are exact zeros
+    }
+  }
+  if (rotate) fwht256_quarter(x, lane);                      // rows past the end rotate zeros: the exchanges stay warp-wide
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[k][c]));
+  }
+  amax = warp_max(amax);
+  if (lane == 0) sm_redk[w] = amax;
+  __syncthreads();
+  float a = sm_redk[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) a = fmaxf(a, sm_redk[i]);
+  a = fmaxf(a, 1e-8f);
+  const float scale = __fdiv_rn(a, qk_i8 ? kInt8Max : kFp8Max);
+  if (threadIdx.x == 0) g.kscale[kvh * g.ntiles_cap + t] = scale;
+
+  const ExactDiv dv = make_exact_div(scale);
+  const int pair = t >> 1, half = t & 1;
+  uint8_t* img = g.k8 + (static_cast<size_t>(kvh) * g.npairs_cap + pair) * kImageBytes;
+  const uint32_t r = half * 64 + lr;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float y[8];
+    div8(dv, x[k], y);
+    const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
+    const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
+    *reinterpret_cast<uint2*>(img + (k >> 2) * kPlaneBytes + swz128(r, (k & 3) * 32 + q * 8)) = make_uint2(lo, hi);
+  }
+}
+
 template <int KV_DTYPE, int IDX_DTYPE>
 __device__ __forceinline__ void kv_transform_item(const Geom& g, int t, int kvh, bool is_v) {
+  __shared__ __align__(16) uint8_t sm_vt[kVStagingBytes];
   uint4 raw[8];
   load_tile_rows<IDX_DTYPE>(g, t, kvh, is_v, raw);
-  transform_tile_rows<KV_DTYPE>(g, t, kvh, is_v, raw);
+  transform_tile_rows<KV_DTYPE>(g, t, kvh, is_v, raw, sm_vt, (is_v ? g.vmean : g.kmean) + kvh * kD + (threadIdx.x & 31) * 8,
+                                is_v ? g.vst[kvh * g.ntiles_cap + t] : 0.f);
 }
 
 template <int KV_DTYPE, int IDX_DTYPE>
@@ -490,74 +561,140 @@ __global__ void __launch_bounds__(kMeansThreads) kv_means_batch_kernel(BatchRef 
   kv_means_head<true>(sg, kvh);
 }
 
-#ifdef AKL_XF_PREFETCH
-// The rows of the CTA's next item are requested before the current item is transformed, so the
-// gather's latency runs under the arithmetic (the transform is bound by instruction issue, the
-// gather by latency; side by side they hide each other).  Only when the next item belongs to
-// another request is its gather issued after the geometry has been swapped.
-template <int KV_DTYPE, int IDX_DTYPE>
-__global__ void __launch_bounds__(kThreads, 2) kv_transform_batch_kernel(BatchRef b) {
-  __shared__ Geom sg;
-  const BatchHeader* hdr = batch_header(b);
-  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = 2 * n_stat;
-  const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
-  int cur = -1;
-  int item = blockIdx.x;
-  if (item >= n_all) return;
-  uint4 raw[8], nxt[8];
-  bool is_v = item >= n_stat;
-  int local = is_v ? item - n_stat : item;
-  int r = find_request(stat_off, n_req, local);
-  stage_geom(b, r, cur, &sg);
-  int in_req = local - __ldg(stat_off + r);
-  load_tile_rows<IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
-  while (true) {
-    const int next = item + static_cast<int>(gridDim.x);
-    bool n_is_v = false, prefetched = false;
-    int n_in_req = 0, n_r = -1;
-    if (next < n_all) {
-      n_is_v = next >= n_stat;
-      const int n_local = n_is_v ? next - n_stat : next;
-      n_r = find_request(stat_off, n_req, n_local);
-      n_in_req = n_local - __ldg(stat_off + n_r);
-      if (n_r == cur) {
-        load_tile_rows<IDX_DTYPE>(sg, n_in_req / sg.Hkv, n_in_req % sg.Hkv, n_is_v, nxt);
-        prefetched = true;
-      }
-    }
-    transform_tile_rows<KV_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
-    __syncthreads();                                   // the item's shared-memory staging is dead
-    if (next >= n_all) break;
-    item = next; is_v = n_is_v; in_req = n_in_req;
-    if (prefetched) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) raw[i] = nxt[i];
+// The transform as a two-stage pipeline.  A CTA owns a contiguous run of items (64-row tile x kv
+// head x {K, V}); the 64 rows of an item are fetched by 64 bulk copies of 512 bytes (lanes 0-7 of
+// each warp fetch the rows that warp will transform) into one of two 32 KB stages, completing on
+// the stage's mbarrier.  While item i is transformed out of one stage, item i+1 is landing in the
+// other, and the copies of item i+2 are issued into i's stage as soon as i is done with it, so
+// every CTA keeps 32-64 KB of reads in flight through all of its arithmetic (three CTAs per SM).
+// The V transpose staging lives in the stage its rows came from.
+struct ItemCursor {
+  int r, lo, hi;      // request r owns the local items [lo, hi)
+};
+
+constexpr int kRowsBytes = kTile * kD * 2;           // 64 rows x 512 bytes
+constexpr int kStageMeanOff = kRowsBytes;            // the kv head's 256 channel means (K or V)
+constexpr int kStageScaleOff = kStageMeanOff + kD * 4;   // V: the tile's scale (one float in a 16-byte slot)
+constexpr int kStageBytes = (kStageScaleOff + 16 + 127) / 128 * 128;
+constexpr int kStageArrivals = kTile + 2;            // one per row, one for the means, one for the scale
+constexpr int kXfStages = 2;
+constexpr long long kXfWaitCycles = 4000000000ll;    // ~2 s: a copy that late is a defect
+static_assert(kVStagingBytes <= kRowsBytes, "the V staging is carved out of a row stage");
+
+template <int IDX_DTYPE>
+__device__ __forceinline__ void fetch_item_rows(const BatchRef& b, const int* stat_off, int n_req, int n_stat, int item,
+                                                ItemCursor& c, uint32_t stage, uint32_t bar) {
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane >= 8 && !(w == 0 && lane < 10)) return;
+  const bool is_v = (item & 1) != 0;                 // K and V of a (tile, kv head) are neighbours: equal work per CTA
+  const int local = item >> 1;
+  if (local < c.lo || local >= c.hi) {
+    c.r = find_request(stat_off, n_req, local);
+    c.lo = __ldg(stat_off + c.r);
+    c.hi = __ldg(stat_off + c.r + 1);
+  }
+  const Geom* gp = reinterpret_cast<const Geom*>(b.table + b.off_geoms + static_cast<size_t>(c.r) * sizeof(Geom));
+  const int hkv = gp->Hkv;
+  const int in_req = local - c.lo;
+  const int t = in_req / hkv, kvh = in_req - t * hkv;
+  if (lane == 8) {            // warp 0: the kv head's channel means ride along with the rows
+    ptx::mbar_expect_tx(bar, kD * 4);
+    ptx::bulk_g2s(stage + kStageMeanOff, (is_v ? gp->vmean : gp->kmean) + kvh * kD, kD * 4, bar);
+    return;
+  }
+  if (lane == 9) {            // warp 0: and the V tile's scale (the arrival is counted in the barrier's total)
+    if (is_v) {
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(stage + kStageScaleOff), "l"(gp->vst + kvh * gp->ntiles_cap + t) : "memory");
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
     } else {
-      stage_geom(b, n_r, cur, &sg);
-      load_tile_rows<IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v, raw);
+      ptx::mbar_arrive(bar);
     }
+    return;
+  }
+  const int row = t * kTile + w * 8 + lane;
+  if (row < gp->N) {
+    const long long p = load_idx<IDX_DTYPE>(gp->idx, row);
+    const uint16_t* pool = reinterpret_cast<const uint16_t*>(is_v ? gp->v_pool : gp->k_pool);
+    ptx::mbar_expect_tx(bar, kD * 2);
+    ptx::bulk_g2s(stage + static_cast<uint32_t>(w * 8 + lane) * (kD * 2), pool + (static_cast<size_t>(p) * hkv + kvh) * kD, kD * 2, bar);
+  } else {
+    ptx::mbar_arrive(bar);          // a row past the end: nothing to copy, the arrival still counts
   }
 }
 
-#else
 template <int KV_DTYPE, int IDX_DTYPE>
 __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRef b) {
+  extern __shared__ __align__(128) uint8_t xf_stages[];      // kXfStages x kStageBytes
   __shared__ Geom sg;
+  __shared__ __align__(8) unsigned long long sm_full[kXfStages];
   const BatchHeader* hdr = batch_header(b);
-  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items;
+  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = 2 * n_stat;
   const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
+  const int per = (n_all + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int item_lo = static_cast<int>(blockIdx.x) * per;
+  const int item_hi = min(item_lo + per, n_all);
+  if (item_lo >= item_hi) return;                            // CTA-uniform
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t stage0 = ptx::smem_u32(xf_stages), bar0 = ptx::smem_u32(sm_full);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kXfStages; ++i) ptx::mbar_init(bar0 + i * 8, kStageArrivals);
+    ptx::mbar_init_fence();
+  }
+  __syncthreads();
+  ItemCursor fc{-1, 0, 0};
+  for (int i = 0; i < kXfStages; ++i)
+    if (item_lo + i < item_hi) fetch_item_rows<IDX_DTYPE>(b, stat_off, n_req, n_stat, item_lo + i, fc, stage0 + i * kStageBytes, bar0 + i * 8);
+
+  ItemCursor cc{-1, 0, 0};
   int cur = -1;
-  for (int item = blockIdx.x; item < 2 * n_stat; item += gridDim.x) {
-    const bool is_v = item >= n_stat;
-    const int local = is_v ? item - n_stat : item;
-    const int r = find_request(stat_off, n_req, local);
-    stage_geom(b, r, cur, &sg);
-    const int in_req = local - __ldg(stat_off + r);
-    kv_transform_item<KV_DTYPE, IDX_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, is_v);
-    __syncthreads();
+  for (int item = item_lo; item < item_hi; ++item) {
+    const int k = item - item_lo, st = k % kXfStages;
+    const uint32_t parity = static_cast<uint32_t>(k / kXfStages) & 1u;
+    const bool is_v = (item & 1) != 0;
+    const int local = item >> 1;
+    if (local < cc.lo || local >= cc.hi) {
+      cc.r = find_request(stat_off, n_req, local);
+      cc.lo = __ldg(stat_off + cc.r);
+      cc.hi = __ldg(stat_off + cc.r + 1);
+    }
+    stage_geom(b, cc.r, cur, &sg);
+    const int in_req = local - cc.lo;
+    const int t = in_req / sg.Hkv, kvh = in_req % sg.Hkv;
+
+    // the rows have landed (bounded: a copy that never completes ends the CTA with a status code)
+    bool ok = true;
+    if (!ptx::mbar_try_wait(bar0 + st * 8, parity)) {
+      const long long t0 = clock64();
+      while (!ptx::mbar_try_wait(bar0 + st * 8, parity)) {
+        if (clock64() - t0 > kXfWaitCycles) { ok = false; break; }
+      }
+    }
+    const uint8_t* stage = xf_stages + st * kStageBytes;
+    if (!is_v) {
+      if (!__syncthreads_and(ok)) {
+        if (threadIdx.x == 0) atomicCAS(sg.status, 0, AKL_ERR_TIMEOUT);
+        return;
+      }
+      transform_k_tile_staged<KV_DTYPE>(sg, t, kvh, stage, reinterpret_cast<const float*>(stage + kStageMeanOff));
+    } else {
+      uint4 raw[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(stage + (w * 8 + i) * (kD * 2) + lane * 16);
+      // every thread holds its rows: the stage may now serve as the V staging
+      if (!__syncthreads_and(ok)) {
+        if (threadIdx.x == 0) atomicCAS(sg.status, 0, AKL_ERR_TIMEOUT);
+        return;
+      }
+      const float* st_mean = reinterpret_cast<const float*>(stage + kStageMeanOff) + lane * 8;
+      const float v_scale = *reinterpret_cast<const float*>(stage + kStageScaleOff);
+      transform_tile_rows<KV_DTYPE>(sg, t, kvh, true, raw, xf_stages + st * kStageBytes, st_mean, v_scale);
+    }
+    ptx::fence_async_smem();                             // generic accesses to the stage before the copies that overwrite it
+    __syncthreads();                                     // the item is done with its stage
+    if (item + kXfStages < item_hi)
+      fetch_item_rows<IDX_DTYPE>(b, stat_off, n_req, n_stat, item + kXfStages, fc, stage0 + st * kStageBytes, bar0 + st * 8);
   }
 }
-#endif
 
 // ---------------------------------------------------------------------------
 // Self-test of the shared-divisor division: every dividend significand (2^23 of them) in four
@@ -680,20 +817,37 @@ int launch_batch_means(const BatchRef& b, int kv_heads, cudaStream_t s) {
   return AKL_OK;
 }
 
+// Opts the four instantiations into their dynamic shared memory, once per device.
+static int configure_transform_once() {
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { note_cuda_error(e, "cudaGetDevice"); return AKL_ERR_CUDA; }
+  if (dev >= 0 && dev < 64 && configured[dev].load(std::memory_order_acquire)) return AKL_OK;
+  const void* kernels[4] = {
+      reinterpret_cast<const void*>(kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I64>), reinterpret_cast<const void*>(kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I32>),
+      reinterpret_cast<const void*>(kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I64>), reinterpret_cast<const void*>(kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I32>)};
+  for (const void* k : kernels) {
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kXfStages * kStageBytes);
+    if (e != cudaSuccess) { note_cuda_error(e, "cudaFuncSetAttribute(transform)"); return AKL_ERR_CUDA; }
+  }
+  if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+  return AKL_OK;
+}
+
 int launch_batch_transform(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
-#ifdef AKL_XF_PREFETCH
-  const unsigned grid = static_cast<unsigned>(sm_count) * 2u;        // two resident CTAs per SM
-#else
+  const int rc = configure_transform_once();
+  if (rc != AKL_OK) return rc;
   const unsigned grid = static_cast<unsigned>(sm_count) * 3u;        // three resident CTAs per SM
-#endif
+  const size_t smem = kXfStages * kStageBytes;
   if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
-    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, smem, s>>>(b);
   else if (kv_dtype == AKL_KV_BF16)
-    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+    kv_transform_batch_kernel<AKL_KV_BF16, AKL_IDX_I32><<<grid, kThreads, smem, s>>>(b);
   else if (idx_dtype == AKL_IDX_I64)
-    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
+    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I64><<<grid, kThreads, smem, s>>>(b);
   else
-    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, 0, s>>>(b);
+    kv_transform_batch_kernel<AKL_KV_FP16, AKL_IDX_I32><<<grid, kThreads, smem, s>>>(b);
   AKL_LAUNCH_CHECK("kv_transform_batch");
   return AKL_OK;
 }
