@@ -520,30 +520,25 @@ __device__ __forceinline__ void stage_geom(const BatchRef& b, int r, int& cur, G
   cur = r;
 }
 
-// The per-item bodies are called, not inlined, in the batch kernels: the loop state then lives
+// The per-item body is called, not inlined, in the batch kernel: the loop state then lives
 // across a call boundary instead of competing with the body for registers.
 template <int KV_DTYPE, int IDX_DTYPE>
-__device__ __noinline__ void stats_or_q_item(const Geom& g, int in_req, bool is_q) {
-  if (is_q) quantize_q_rows(g, in_req);
-  else kv_tile_stats_item<KV_DTYPE, IDX_DTYPE>(g, in_req);
+__device__ __noinline__ void stats_item(const Geom& g, int in_req) {
+  kv_tile_stats_item<KV_DTYPE, IDX_DTYPE>(g, in_req);
 }
 
+// Tile statistics of the whole batch (the Q quantisation runs in the transform launch).
 template <int KV_DTYPE, int IDX_DTYPE>
-__global__ void __launch_bounds__(kThreads, 3) kv_tile_stats_batch_kernel(BatchRef b) {
+__global__ void __launch_bounds__(kThreads, 4) kv_tile_stats_batch_kernel(BatchRef b) {
   __shared__ Geom sg;
   const BatchHeader* hdr = batch_header(b);
-  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = n_stat + hdr->n_q_ctas;
+  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items;
   const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
-  const int* qcta_off = reinterpret_cast<const int*>(b.table + b.off_qcta_off);
   int cur = -1;
-  for (int item = blockIdx.x; item < n_all; item += gridDim.x) {
-    const bool is_q = item >= n_stat;
-    const int local = is_q ? item - n_stat : item;
-    const int* totals = is_q ? qcta_off : stat_off;
-    const int r = find_request(totals, n_req, local);
+  for (int item = blockIdx.x; item < n_stat; item += gridDim.x) {
+    const int r = find_request(stat_off, n_req, item);
     stage_geom(b, r, cur, &sg);
-    const int in_req = local - __ldg(totals + r);
-    stats_or_q_item<KV_DTYPE, IDX_DTYPE>(sg, in_req, is_q);
+    stats_item<KV_DTYPE, IDX_DTYPE>(sg, item - __ldg(stat_off + r));
     __syncthreads();                                 // the item's shared-memory partials are dead
   }
 }
@@ -561,15 +556,68 @@ __global__ void __launch_bounds__(kMeansThreads) kv_means_batch_kernel(BatchRef 
   kv_means_head<true>(sg, kvh);
 }
 
-// The transform as a two-stage pipeline.  A CTA owns a contiguous run of items (64-row tile x kv
-// head x {K, V}); the 64 rows of an item are fetched by 64 bulk copies of 512 bytes (lanes 0-7 of
-// each warp fetch the rows that warp will transform) into one of two 32 KB stages, completing on
-// the stage's mbarrier.  While item i is transformed out of one stage, item i+1 is landing in the
-// other, and the copies of item i+2 are issued into i's stage as soon as i is done with it, so
-// every CTA keeps 32-64 KB of reads in flight through all of its arithmetic (three CTAs per SM).
-// The V transpose staging lives in the stage its rows came from.
+// Q out of a row stage: 64 rows of one head (half of a 128-row tile), a row spread over four lanes
+// as in transform_k_tile_staged; per-row amax over the four lanes, per-row divisor.  Same bytes and
+// scales as quantize_q_rows.  Rows >= T are zero bytes with the clamp scale.
+__device__ __forceinline__ void quantize_q_half_staged(const Geom& g, int head, int tile, int half, const uint8_t* rows) {
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane & 3, lr = half * 64 + w * 8 + (lane >> 2);     // row inside the 128-row tile
+  const int r = tile * kQTile + lr;
+  const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
+  const bool rotate = (g.flags & AKL_FLAG_ROTATE) != 0;
+  float x[8][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (r < g.T) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(rows + (lr & 63) * (kD * 2) + k * 64 + q * 16);
+      unpack8<AKL_KV_BF16>(raw, x[k]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) x[k][c] = 0.f;
+    }
+  }
+  if (rotate) fwht256_quarter(x, lane);
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) amax = fmaxf(amax, fabsf(x[k][c]));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, 1e-8f);
+  const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
+  const ExactDiv dv = make_exact_div(scale);
+  uint8_t* img = g.q8 + (static_cast<size_t>(head) * g.mtiles_cap + tile) * kImageBytes;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float y[8];
+    div8(dv, x[k], y);
+    const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
+    const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
+    *reinterpret_cast<uint2*>(img + (k >> 2) * kPlaneBytes + swz128(lr, (k & 3) * 32 + q * 8)) = make_uint2(lo, hi);
+  }
+  if (q == 0) g.qscale[static_cast<size_t>(head) * g.mtiles_cap * kQTile + r] = __fmul_rn(scale, g.sm_scale);
+}
+
+// The transform as a two-stage pipeline.  A CTA owns a contiguous run of items: (64-row tile x kv
+// head x {K, V}) and, after them, (64 rows of a Q head) - the Q quantisation needs nothing from the
+// statistics and is the same arithmetic as K.  The 64 rows of an item are fetched by 64 bulk
+// copies of 512 bytes (lanes 0-7 of each warp fetch eight rows each) into one of two 33 KB stages,
+// completing on the stage's mbarrier; the kv head's channel means and the V tile's scale ride
+// along.  While item i is transformed out of one stage, item i+1 is landing in the other, and the
+// copies of item i+2 are issued into i's stage as soon as i is done with it, so every CTA keeps
+// 32-64 KB of reads in flight through all of its arithmetic (three CTAs per SM).  The V transpose
+// staging lives in the stage its rows came from.
 struct ItemCursor {
-  int r, lo, hi;      // request r owns the local items [lo, hi)
+  int space;          // 0: (tile, kv head) items, running totals stat_off; 1: Q CTAs, totals qcta_off
+  int r, lo, hi;      // request r owns the local items [lo, hi) of that space
+};
+
+struct ItemSpace {
+  const int* stat_off;
+  const int* qcta_off;
+  int n_req, n_kv, n_all;     // items [0, n_kv): K/V; [n_kv, n_all): Q halves
 };
 
 constexpr int kRowsBytes = kTile * kD * 2;           // 64 rows x 512 bytes
@@ -580,22 +628,58 @@ constexpr int kStageArrivals = kTile + 2;            // one per row, one for the
 constexpr int kXfStages = 2;
 constexpr long long kXfWaitCycles = 4000000000ll;    // ~2 s: a copy that late is a defect
 static_assert(kVStagingBytes <= kRowsBytes, "the V staging is carved out of a row stage");
+// relative cost of an item, for the split of the item range over the CTAs
+constexpr int kCostKV = 5;                           // a K item and its V neighbour together
+constexpr int kCostQ = 3;
+
+// kind: 0 K, 1 V, 2 Q.  Returns the index inside the request (tile * Hkv + kv head, or Q CTA) and,
+// for Q, which half of the 128-row tile.
+__device__ __forceinline__ int locate_item(const ItemSpace& sp, int item, ItemCursor& c, int& kind, int& half) {
+  int space, local;
+  if (item < sp.n_kv) {
+    kind = item & 1;                                 // K and V of a (tile, kv head) are neighbours
+    half = 0;
+    space = 0;
+    local = item >> 1;
+  } else {
+    kind = 2;
+    half = (item - sp.n_kv) & 1;
+    space = 1;
+    local = (item - sp.n_kv) >> 1;
+  }
+  if (c.space != space || local < c.lo || local >= c.hi) {
+    const int* totals = space ? sp.qcta_off : sp.stat_off;
+    c.space = space;
+    c.r = find_request(totals, sp.n_req, local);
+    c.lo = __ldg(totals + c.r);
+    c.hi = __ldg(totals + c.r + 1);
+  }
+  return local - c.lo;
+}
 
 template <int IDX_DTYPE>
-__device__ __forceinline__ void fetch_item_rows(const BatchRef& b, const int* stat_off, int n_req, int n_stat, int item,
-                                                ItemCursor& c, uint32_t stage, uint32_t bar) {
+__device__ __forceinline__ void fetch_item_rows(const BatchRef& b, const ItemSpace& sp, int item, ItemCursor& c, uint32_t stage, uint32_t bar) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (lane >= 8 && !(w == 0 && lane < 10)) return;
-  const bool is_v = (item & 1) != 0;                 // K and V of a (tile, kv head) are neighbours: equal work per CTA
-  const int local = item >> 1;
-  if (local < c.lo || local >= c.hi) {
-    c.r = find_request(stat_off, n_req, local);
-    c.lo = __ldg(stat_off + c.r);
-    c.hi = __ldg(stat_off + c.r + 1);
-  }
+  int kind, half;
+  const int in_req = locate_item(sp, item, c, kind, half);
   const Geom* gp = reinterpret_cast<const Geom*>(b.table + b.off_geoms + static_cast<size_t>(c.r) * sizeof(Geom));
+  if (kind == 2) {
+    if (lane >= 8) { ptx::mbar_arrive(bar); return; }          // no means, no scale: the arrivals still count
+    const int mt = gp->mtiles;
+    const int head = in_req / mt, tile = in_req - head * mt;
+    const int row = tile * kQTile + half * 64 + w * 8 + lane;
+    if (row < gp->T && head < gp->Hq) {
+      ptx::mbar_expect_tx(bar, kD * 2);
+      ptx::bulk_g2s(stage + static_cast<uint32_t>(w * 8 + lane) * (kD * 2),
+                    reinterpret_cast<const uint16_t*>(gp->q) + (static_cast<size_t>(row) * gp->Hq + head) * kD, kD * 2, bar);
+    } else {
+      ptx::mbar_arrive(bar);
+    }
+    return;
+  }
+  const bool is_v = kind == 1;
   const int hkv = gp->Hkv;
-  const int in_req = local - c.lo;
   const int t = in_req / hkv, kvh = in_req - t * hkv;
   if (lane == 8) {            // warp 0: the kv head's channel means ride along with the rows
     ptx::mbar_expect_tx(bar, kD * 4);
@@ -622,17 +706,30 @@ __device__ __forceinline__ void fetch_item_rows(const BatchRef& b, const int* st
   }
 }
 
+// Item index at cost position x (costs: kCostKV per K/V pair, kCostQ per Q half).
+__device__ __forceinline__ int item_at_cost(long long x, int n_kv, int n_all) {
+  const long long kv_cost = static_cast<long long>(n_kv / 2) * kCostKV;
+  if (x < kv_cost) return static_cast<int>(x / kCostKV) * 2;
+  const long long i = n_kv + (x - kv_cost) / kCostQ;
+  return static_cast<int>(i < n_all ? i : n_all);
+}
+
 template <int KV_DTYPE, int IDX_DTYPE>
 __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRef b) {
   extern __shared__ __align__(128) uint8_t xf_stages[];      // kXfStages x kStageBytes
   __shared__ Geom sg;
   __shared__ __align__(8) unsigned long long sm_full[kXfStages];
   const BatchHeader* hdr = batch_header(b);
-  const int n_req = hdr->n_requests, n_stat = hdr->n_stat_items, n_all = 2 * n_stat;
-  const int* stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
-  const int per = (n_all + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int item_lo = static_cast<int>(blockIdx.x) * per;
-  const int item_hi = min(item_lo + per, n_all);
+  ItemSpace sp;
+  sp.stat_off = reinterpret_cast<const int*>(b.table + b.off_stat_off);
+  sp.qcta_off = reinterpret_cast<const int*>(b.table + b.off_qcta_off);
+  sp.n_req = hdr->n_requests;
+  sp.n_kv = 2 * hdr->n_stat_items;
+  sp.n_all = sp.n_kv + 2 * hdr->n_q_ctas;
+  const long long total_cost = static_cast<long long>(hdr->n_stat_items) * kCostKV + static_cast<long long>(2 * hdr->n_q_ctas) * kCostQ;
+  const long long g_ = gridDim.x, c_ = blockIdx.x;
+  const int item_lo = item_at_cost(total_cost * c_ / g_, sp.n_kv, sp.n_all);
+  const int item_hi = (c_ + 1 == g_) ? sp.n_all : item_at_cost(total_cost * (c_ + 1) / g_, sp.n_kv, sp.n_all);
   if (item_lo >= item_hi) return;                            // CTA-uniform
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t stage0 = ptx::smem_u32(xf_stages), bar0 = ptx::smem_u32(sm_full);
@@ -641,25 +738,18 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
     ptx::mbar_init_fence();
   }
   __syncthreads();
-  ItemCursor fc{-1, 0, 0};
+  ItemCursor fc{-1, -1, 0, 0};
   for (int i = 0; i < kXfStages; ++i)
-    if (item_lo + i < item_hi) fetch_item_rows<IDX_DTYPE>(b, stat_off, n_req, n_stat, item_lo + i, fc, stage0 + i * kStageBytes, bar0 + i * 8);
+    if (item_lo + i < item_hi) fetch_item_rows<IDX_DTYPE>(b, sp, item_lo + i, fc, stage0 + i * kStageBytes, bar0 + i * 8);
 
-  ItemCursor cc{-1, 0, 0};
+  ItemCursor cc{-1, -1, 0, 0};
   int cur = -1;
   for (int item = item_lo; item < item_hi; ++item) {
     const int k = item - item_lo, st = k % kXfStages;
     const uint32_t parity = static_cast<uint32_t>(k / kXfStages) & 1u;
-    const bool is_v = (item & 1) != 0;
-    const int local = item >> 1;
-    if (local < cc.lo || local >= cc.hi) {
-      cc.r = find_request(stat_off, n_req, local);
-      cc.lo = __ldg(stat_off + cc.r);
-      cc.hi = __ldg(stat_off + cc.r + 1);
-    }
+    int kind, half;
+    const int in_req = locate_item(sp, item, cc, kind, half);
     stage_geom(b, cc.r, cur, &sg);
-    const int in_req = local - cc.lo;
-    const int t = in_req / sg.Hkv, kvh = in_req % sg.Hkv;
 
     // the rows have landed (bounded: a copy that never completes ends the CTA with a status code)
     bool ok = true;
@@ -670,12 +760,16 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
       }
     }
     const uint8_t* stage = xf_stages + st * kStageBytes;
-    if (!is_v) {
+    if (kind != 1) {
       if (!__syncthreads_and(ok)) {
         if (threadIdx.x == 0) atomicCAS(sg.status, 0, AKL_ERR_TIMEOUT);
         return;
       }
-      transform_k_tile_staged<KV_DTYPE>(sg, t, kvh, stage, reinterpret_cast<const float*>(stage + kStageMeanOff));
+      if (kind == 0) {
+        transform_k_tile_staged<KV_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, stage, reinterpret_cast<const float*>(stage + kStageMeanOff));
+      } else {
+        quantize_q_half_staged(sg, in_req / sg.mtiles, in_req % sg.mtiles, half, stage);
+      }
     } else {
       uint4 raw[8];
 #pragma unroll
@@ -687,12 +781,12 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
       }
       const float* st_mean = reinterpret_cast<const float*>(stage + kStageMeanOff) + lane * 8;
       const float v_scale = *reinterpret_cast<const float*>(stage + kStageScaleOff);
-      transform_tile_rows<KV_DTYPE>(sg, t, kvh, true, raw, xf_stages + st * kStageBytes, st_mean, v_scale);
+      transform_tile_rows<KV_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, true, raw, xf_stages + st * kStageBytes, st_mean, v_scale);
     }
     ptx::fence_async_smem();                             // generic accesses to the stage before the copies that overwrite it
     __syncthreads();                                     // the item is done with its stage
     if (item + kXfStages < item_hi)
-      fetch_item_rows<IDX_DTYPE>(b, stat_off, n_req, n_stat, item + kXfStages, fc, stage0 + st * kStageBytes, bar0 + st * 8);
+      fetch_item_rows<IDX_DTYPE>(b, sp, item + kXfStages, fc, stage0 + st * kStageBytes, bar0 + st * 8);
   }
 }
 
@@ -798,7 +892,7 @@ int launch_kv_transform(const Geom& g, int kv_dtype, int idx_dtype, cudaStream_t
 }
 
 int launch_batch_stats(const BatchRef& b, int kv_dtype, int idx_dtype, int sm_count, cudaStream_t s) {
-  const unsigned grid = static_cast<unsigned>(sm_count) * 3u;        // three resident CTAs per SM
+  const unsigned grid = static_cast<unsigned>(sm_count) * 4u;        // four resident CTAs per SM
   if (kv_dtype == AKL_KV_BF16 && idx_dtype == AKL_IDX_I64)
     kv_tile_stats_batch_kernel<AKL_KV_BF16, AKL_IDX_I64><<<grid, kThreads, 0, s>>>(b);
   else if (kv_dtype == AKL_KV_BF16)

@@ -271,14 +271,15 @@ def phase_rooflines(torch, K, stepper, wl, peaks, fp8_peak):
     ws.launch(plan)
     torch.cuda.synchronize()
     ms = {}
-    for name, mask in (("stats_q", K.AKL_BATCH_STATS), ("means", K.AKL_BATCH_MEANS),
+    for name, mask in (("stats", K.AKL_BATCH_STATS), ("means", K.AKL_BATCH_MEANS),
                        ("transform", K.AKL_BATCH_TRANSFORM), ("attention", K.AKL_BATCH_ATTENTION)):
         ms[name] = device_time(torch, lambda: ws.launch(plan, phases=mask, upload=False), reps=10)
     reqs = wl["reqs"]
     sum_n, sum_t = sum(r["N"] for r in reqs), sum(r["T"] for r in reqs)
     kv_rows = 2 * sum_n * HKV * D * 2                      # one read of the request's K and V rows
-    bytes_ = {"stats_q": kv_rows + sum_t * HQ * D * 2 + sum_t * HQ * D + sum_n * 8,   # + Q read, Q8 write, idx
-              "transform": kv_rows + 2 * sum_n * HKV * D + sum_n * 8}                  # rows again, K8 + V8 write
+    bytes_ = {"stats": kv_rows + sum_n * 8,                                           # K and V rows once + page table
+              # the rows again, K8 + V8 write, page table; Q read and Q8 write (the Q quantisation runs in this launch)
+              "transform": kv_rows + 2 * sum_n * HKV * D + sum_n * 8 + sum_t * HQ * D * 3}
     attn_flops = sum(flops(r["prefix"], r["T"]) for r in reqs)
     achieved = attn_flops / ms["attention"] / 1e9
     peak = fp8_peak if fp8_peak else 2.0 * peaks["bf16_tflops"]
@@ -303,7 +304,7 @@ def phase_rooflines(torch, K, stepper, wl, peaks, fp8_peak):
             "prep": {name: {"ms_per_launch": ms[name], "algorithmic_bytes": bytes_[name],
                             "achieved": bytes_[name] / ms[name] / 1e6, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": bytes_[name] / ms[name] / 1e6 / peaks["hbm_gbs"]}
-                     for name in ("stats_q", "transform")},
+                     for name in ("stats", "transform")},
             "means_ms_per_launch": ms["means"]}
     return roof
 
@@ -439,7 +440,7 @@ def c5_serving(torch, dist, pkg, K, syn, dev, rank: int, world: int, peaks, reps
     replay = capture(torch, lambda: ws.launch(plan))
     ms_batch = device_time(torch, replay, reps=reps)
     phases = {}
-    for name, mask in (("stats_q", K.AKL_BATCH_STATS), ("means", K.AKL_BATCH_MEANS),
+    for name, mask in (("stats", K.AKL_BATCH_STATS), ("means", K.AKL_BATCH_MEANS),
                        ("transform", K.AKL_BATCH_TRANSFORM), ("attention", K.AKL_BATCH_ATTENTION)):
         phases[name] = device_time(torch, lambda: ws.launch(plan, phases=mask, upload=False), reps=3, warm=1)
     if ws.status() != 0:
@@ -453,7 +454,7 @@ def c5_serving(torch, dist, pkg, K, syn, dev, rank: int, world: int, peaks, reps
     sum_n = sum(p + t_ for p, t_ in lens)
     kv_rows = 2 * sum_n * HKV * D * 2
     step_bytes = kv_rows + 2 * total_t * HQ * D * 2 + sum_n * 8
-    prep_bytes = {"stats_q": kv_rows + total_t * HQ * D * 3 + sum_n * 8, "transform": kv_rows + 2 * sum_n * HKV * D + sum_n * 8}
+    prep_bytes = {"stats": kv_rows + sum_n * 8, "transform": kv_rows + 2 * sum_n * HKV * D + sum_n * 8 + total_t * HQ * D * 3}
     del kp, vp
     return {"requests": 256, "requests_this_rank": len(reqs), "partition": f"by request, attended pairs, x{world}",
             "launch": "one CUDA graph of one batched call (table copy + 4 launches), replayed",
@@ -463,7 +464,7 @@ def c5_serving(torch, dist, pkg, K, syn, dev, rank: int, world: int, peaks, reps
             "rank0": {"kv_tokens": sum_n, "extend_tokens": total_t, "phase_ms": phases,
                       "attention_tflops": sum(flops(p, t_) for p, t_ in lens) / phases["attention"] / 1e9,
                       "hbm_frac_of_prep": {name: prep_bytes[name] / phases[name] / 1e6 / peaks["hbm_gbs"]
-                                           for name in ("stats_q", "transform")},
+                                           for name in ("stats", "transform")},
                       "hbm_frac_whole_batch": step_bytes / ms_batch / 1e6 / peaks["hbm_gbs"]}}
 
 

@@ -247,9 +247,9 @@ int akl_prefill_extend_batch(const akl_batch_t* b, void* stream);
 
 /* A subset of the batch's launches, in their fixed order, for callers that put their own work
  * between them and for per-phase timing: the batched counterpart of the phase entry points above. */
-#define AKL_BATCH_STATS 1u      /* tile statistics + Q quantisation */
+#define AKL_BATCH_STATS 1u      /* K/V tile statistics */
 #define AKL_BATCH_MEANS 2u      /* channel means, V tile scales, fold arrays */
-#define AKL_BATCH_TRANSFORM 4u  /* K/V centre, rotate, quantise */
+#define AKL_BATCH_TRANSFORM 4u  /* K/V centre, rotate, quantise; Q rotate, quantise */
 #define AKL_BATCH_ATTENTION 8u
 #define AKL_BATCH_ALL 15u
 int akl_prefill_extend_batch_phases(const akl_batch_t* b, uint32_t phases, void* stream);
