@@ -392,6 +392,14 @@ int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* reqs, int32_
     g.q = q.q; g.k_pool = q.k_pool; g.v_pool = q.v_pool; g.idx = q.idx; g.out = q.out; g.lse_out = q.lse_out;
     g.q8 = ws + L.off_q8 + mtile_off * kImageBytes;
     g.qscale = reinterpret_cast<float*>(ws + L.off_qscale) + mtile_off * kQTile;
+    // packed Q tiles: the same storage seen as [Hkv][group * MT] tiles; a request's packed tiles
+    // (at most group * mtiles of them) start at group * mtile_off of every kv head's stripe
+    const int group = hq / hkv;
+    g.q8p = ws + L.off_q8 + static_cast<int64_t>(group) * mtile_off * kImageBytes;
+    g.qscalep = reinterpret_cast<float*>(ws + L.off_qscale) + static_cast<int64_t>(group) * mtile_off * kQTile;
+    const int64_t ptiles = (static_cast<int64_t>(q.T) * group + kQTile - 1) / kQTile;
+    if (ptiles >= (1 << 16)) return AKL_ERR_CAPACITY;
+    g.ptiles = static_cast<int>(ptiles);
     g.k8 = ws + L.off_k8 + pair_off * kImageBytes;
     g.v8t = ws + L.off_v8t + pair_off * kImageBytes;
     g.kscale = reinterpret_cast<float*>(ws + L.off_kscale) + tile_off;
@@ -416,7 +424,7 @@ int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* reqs, int32_
     stat_off[r] = static_cast<int32_t>(stat_items);
     qcta_off[r] = static_cast<int32_t>(q_ctas);
     stat_items += nt * hkv;
-    q_ctas += static_cast<int64_t>(hq) * mtiles * kQTile / kQRowsPerCtaHost;
+    q_ctas += static_cast<int64_t>(hkv) * ptiles;             // one per packed 128-row Q tile
     pair_off += npairs;
     mtile_off += mtiles;
     req_cost[r] = static_cast<double>(q.T) * (q.prefix + (q.T + 1) / 2.0);
@@ -426,17 +434,20 @@ int akl_batch_plan(const akl_batch_t* b, const akl_batch_request_t* reqs, int32_
   for (int r = n + 1; r <= b->caps.max_requests; ++r) { stat_off[r] = stat_off[n]; qcta_off[r] = qcta_off[n]; }
 
   // attention work items: requests longest first (so the K/V tiles of one or two requests stay in
-  // L2 while their items run), inside a request the deepest query tiles first, heads together
+  // L2 while their items run), inside a request the deepest packed query tiles first, kv heads
+  // together.  An item is (request, kv head, packed tile): 128 (token, head) rows of one kv head's
+  // group, so a request of T tokens costs ceil(T * group / 128) tiles per kv head instead of
+  // group * ceil(T / 128)
   std::vector<int> order(static_cast<size_t>(n));
   for (int r = 0; r < n; ++r) order[r] = r;
   std::stable_sort(order.begin(), order.end(), [&](int a, int c) { return req_cost[a] > req_cost[c]; });
   int64_t n_items = 0;
   for (int r : order) {
     const Geom& g = geoms[r];
-    for (int qt = g.mtiles - 1; qt >= 0; --qt)
-      for (int h = 0; h < hq; ++h) {
+    for (int pt = g.ptiles - 1; pt >= 0; --pt)
+      for (int kvh = 0; kvh < hkv; ++kvh) {
         items[2 * n_items] = r;
-        items[2 * n_items + 1] = (h << 16) | qt;
+        items[2 * n_items + 1] = (kvh << 16) | pt;
         ++n_items;
       }
   }

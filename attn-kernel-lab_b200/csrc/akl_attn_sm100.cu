@@ -224,9 +224,26 @@ static_assert(8 * 32 * kRegsSoftmax + 8 * 32 * kRegsStart + 4 * 32 * kRegsMisc <
               "register budget: an increase waits for registers other warps never release");
 
 // What one (q tile, q head) work item needs, derived by every thread for itself.
+// kBatch = false: the 128 rows of an item are the tokens m0 .. m0+127 of q head h.  kBatch = true:
+// they are 128 consecutive PACKED rows of kv head kvh, row R = qt * 128 + r standing for token
+// R / group and q head kvh * group + R % group (group = Hq / Hkv), so that short requests do not
+// pay a 128-row tile per q head.
 struct Item {
-  int qt, h, kvh, m0, ntile, npair;
+  int qt, h, kvh, m0, ntile, npair, group;
 };
+
+// Token and q head of row `row` of the item.
+template <bool kBatch>
+__device__ __forceinline__ void item_row(const Item& it, int row, int& token, int& head) {
+  if (kBatch) {
+    const int R = it.qt * kQTile + row;
+    token = R / it.group;
+    head = it.kvh * it.group + (R - token * it.group);
+  } else {
+    token = it.m0 + row;
+    head = it.h;
+  }
+}
 
 struct Shared {
   uint32_t tmem_slot;
@@ -256,7 +273,8 @@ __device__ __forceinline__ bool begin_item(const Geom& g, const BatchRef& bref, 
     const int item = sh.item;
     if (item >= hdr->n_attn_items || sh.abort_flag != 0) return false;     // CTA-uniform
     const int2 w = sh.word;
-    it.h = w.y >> 16;
+    it.h = 0;
+    it.kvh = w.y >> 16;
     it.qt = w.y & 0xFFFF;
     if (w.x != cur_request) {
       const uint32_t* src = reinterpret_cast<const uint32_t*>(bref.table + bref.off_geoms + static_cast<size_t>(w.x) * sizeof(Geom));
@@ -296,10 +314,12 @@ __device__ __forceinline__ bool begin_item(const Geom& g, const BatchRef& bref, 
     __syncthreads();                    // the staged geometry is visible
     if (tid == 0) drawn = atomicAdd(&batch_header(bref)->attn_counter, 1);
   }
-  it.kvh = it.h / (g.Hq / g.Hkv);
+  it.group = g.Hq / g.Hkv;
+  if (!kBatch) it.kvh = it.h / it.group;
   it.m0 = it.qt * kQTile;
-  // keys this item visits, in local (this call's) positions
-  long long hi_ll = static_cast<long long>(g.prefix) + it.m0 + kQTile - g.kv_pos0;
+  // keys this item visits, in local (this call's) positions: up to the last token of the item
+  const int tok_end = kBatch ? (it.qt * kQTile + kQTile - 1) / it.group + 1 : it.m0 + kQTile;
+  long long hi_ll = static_cast<long long>(g.prefix) + tok_end - g.kv_pos0;
   const int hi = static_cast<int>(hi_ll < 0 ? 0 : (hi_ll > g.N ? g.N : hi_ll));
   it.ntile = (hi + kTile - 1) / kTile;
   it.npair = (it.ntile + 1) / 2;
@@ -353,7 +373,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
       if (lane != 0 || ntile == 0) continue;
       if (warp == kProducerWarp) {
         // ---------------------------------------------------------- Q and K copies
-        const uint8_t* qsrc = g.q8 + (static_cast<size_t>(it.h) * g.mtiles_cap + it.qt) * kImageBytes;
+        const uint8_t* qsrc = kBatch
+            ? g.q8p + (static_cast<size_t>(it.kvh) * it.group * g.mtiles_cap + it.qt) * kImageBytes
+            : g.q8 + (static_cast<size_t>(it.h) * g.mtiles_cap + it.qt) * kImageBytes;
         const uint8_t* ksrc = g.k8 + static_cast<size_t>(it.kvh) * g.npairs_cap * kImageBytes;
         mbar_expect_tx(ctx.bars + B_QFULL * 8, kImageBytes);
         bulk_g2s(smem + kOffQ, qsrc, kImageBytes, ctx.bars + B_QFULL * 8);
@@ -465,11 +487,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_sm100_kernel(const __grid_co
     float* sm_alpha = reinterpret_cast<float*>(smem_gen + kOffAlpha);
     for (int iter = 0; begin_item<kBatch>(g, bref, sh, smem, smem_gen, iter, cur_request, drawn, it); ++iter) {
     ctx.status = g.status;
-    const int ntile = it.ntile, h = it.h, kvh = it.kvh, qt = it.qt;
-    const int grow = it.m0 + row;
+    const int ntile = it.ntile, kvh = it.kvh, qt = it.qt;
+    int grow, h;                                 // this row's token and q head
+    item_row<kBatch>(it, row, grow, h);
     long long lim_ll = static_cast<long long>(g.prefix) + grow - g.kv_pos0;
     const int limit = static_cast<int>(lim_ll > g.N - 1 ? g.N - 1 : lim_ll);   // last visible local key (may be < 0)
-    const float qs = g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
+    const float qs = kBatch
+        ? g.qscalep[(static_cast<size_t>(kvh) * it.group * g.mtiles_cap + qt) * kQTile + row]
+        : g.qscale[static_cast<size_t>(h) * g.mtiles_cap * kQTile + grow];
     const float* kscale = g.kscale + kvh * g.ntiles_cap;
     const float* vlog2r = g.vlog2r + kvh * g.ntiles_cap;
     const float* vinvr = g.vinvr + kvh * g.ntiles_cap;

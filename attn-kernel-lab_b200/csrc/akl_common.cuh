@@ -31,6 +31,10 @@ struct Geom {
   float* lse_out;
   uint8_t* q8;
   float* qscale;
+  // batched entry only: Q rows of the q heads that share a kv head packed into common 128-row
+  // tiles, row R = token * (Hq / Hkv) + (head inside the group); images [Hkv][group * mtiles_cap]
+  uint8_t* q8p;
+  float* qscalep;
   uint8_t* k8;
   uint8_t* v8t;
   float* kscale;
@@ -53,6 +57,7 @@ struct Geom {
   int npairs_cap, ntiles_cap, mtiles_cap;
   int nt;          // local 64-row tiles = ceil(N / 64)
   int mtiles;      // ceil(T / 128)
+  int ptiles;      // batched entry: packed Q tiles per kv head = ceil(T * (Hq / Hkv) / 128)
   int kv_pos0, n_total, tile0_global, ntiles_global;
   unsigned flags;
   float sm_scale;
@@ -63,13 +68,13 @@ struct Geom {
 //   BatchHeader | Geom[max_requests] | stat_off[max_requests + 1] | qcta_off[max_requests + 1]
 //   | attention work items (int2 {request, q head << 16 | q tile}), longest first.
 // stat_off / qcta_off are running totals of the statistics items (64-row tile x kv head) and
-// of the Q-quantisation CTAs per request, so a flat item index is mapped back to its request
-// by a binary search.
+// of the packed Q tiles (128 (token, head) rows of one kv head's group) per request, so a flat
+// item index is mapped back to its request by a binary search.
 struct BatchHeader {
   int32_t magic;
   int32_t n_requests;
   int32_t n_stat_items;
-  int32_t n_q_ctas;
+  int32_t n_q_ctas;       // packed Q tiles over all requests (each is quantised as two 64-row items)
   int32_t n_attn_items;
   int32_t attn_counter;   // device side: next attention work item (reset by the means launch)
   int32_t reserved[10];

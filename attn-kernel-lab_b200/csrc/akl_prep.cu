@@ -556,20 +556,24 @@ __global__ void __launch_bounds__(kMeansThreads) kv_means_batch_kernel(BatchRef 
   kv_means_head<true>(sg, kvh);
 }
 
-// Q out of a row stage: 64 rows of one head (half of a 128-row tile), a row spread over four lanes
-// as in transform_k_tile_staged; per-row amax over the four lanes, per-row divisor.  Same bytes and
-// scales as quantize_q_rows.  Rows >= T are zero bytes with the clamp scale.
-__device__ __forceinline__ void quantize_q_half_staged(const Geom& g, int head, int tile, int half, const uint8_t* rows) {
+// Q out of a row stage: 64 consecutive PACKED rows of one kv head's group of q heads (half of a
+// packed 128-row tile; row R stands for token R / group and head kvh * group + R % group), a row
+// spread over four lanes as in transform_k_tile_staged; per-row amax over the four lanes, per-row
+// divisor.  Same bytes and scales per row as quantize_q_rows.  Rows of tokens >= T are zero bytes
+// with the clamp scale.  The batched attention launch reads 128 such rows per work item.
+__device__ __forceinline__ void quantize_q_half_staged(const Geom& g, int kvh, int pt, int half, const uint8_t* rows) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = lane & 3, lr = half * 64 + w * 8 + (lane >> 2);     // row inside the 128-row tile
-  const int r = tile * kQTile + lr;
+  const int q = lane & 3, lr = w * 8 + (lane >> 2);              // row inside the 64-row stage
+  const int group = g.Hq / g.Hkv;
+  const int R = pt * kQTile + half * 64 + lr;
+  const bool live = R / group < g.T;
   const bool qk_i8 = (g.flags & AKL_FLAG_QK_I8) != 0;
   const bool rotate = (g.flags & AKL_FLAG_ROTATE) != 0;
   float x[8][8];
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    if (r < g.T) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(rows + (lr & 63) * (kD * 2) + k * 64 + q * 16);
+    if (live) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(rows + lr * (kD * 2) + k * 64 + q * 16);
       unpack8<AKL_KV_BF16>(raw, x[k]);
     } else {
 #pragma unroll
@@ -588,20 +592,22 @@ __device__ __forceinline__ void quantize_q_half_staged(const Geom& g, int head, 
   amax = fmaxf(amax, 1e-8f);
   const float scale = __fdiv_rn(amax, qk_i8 ? kInt8Max : kFp8Max);
   const ExactDiv dv = make_exact_div(scale);
-  uint8_t* img = g.q8 + (static_cast<size_t>(head) * g.mtiles_cap + tile) * kImageBytes;
+  const size_t stripe = static_cast<size_t>(group) * g.mtiles_cap;  // packed tiles in a kv head's stripe
+  uint8_t* img = g.q8p + (static_cast<size_t>(kvh) * stripe + pt) * kImageBytes;
+  const uint32_t prow = half * 64 + lr;
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     float y[8];
     div8(dv, x[k], y);
     const uint32_t lo = cvt_qk_x4(qk_i8, y[0], y[1], y[2], y[3]);
     const uint32_t hi = cvt_qk_x4(qk_i8, y[4], y[5], y[6], y[7]);
-    *reinterpret_cast<uint2*>(img + (k >> 2) * kPlaneBytes + swz128(lr, (k & 3) * 32 + q * 8)) = make_uint2(lo, hi);
+    *reinterpret_cast<uint2*>(img + (k >> 2) * kPlaneBytes + swz128(prow, (k & 3) * 32 + q * 8)) = make_uint2(lo, hi);
   }
-  if (q == 0) g.qscale[static_cast<size_t>(head) * g.mtiles_cap * kQTile + r] = __fmul_rn(scale, g.sm_scale);
+  if (q == 0) g.qscalep[static_cast<size_t>(kvh) * stripe * kQTile + R] = __fmul_rn(scale, g.sm_scale);
 }
 
 // The transform as a two-stage pipeline.  A CTA owns a contiguous run of items: (64-row tile x kv
-// head x {K, V}) and, after them, (64 rows of a Q head) - the Q quantisation needs nothing from the
+// head x {K, V}) and, after them, (64 packed Q rows of a kv head) - the Q quantisation needs nothing from the
 // statistics and is the same arithmetic as K.  The 64 rows of an item are fetched by 64 bulk
 // copies of 512 bytes (lanes 0-7 of each warp fetch eight rows each) into one of two 33 KB stages,
 // completing on the stage's mbarrier; the kv head's channel means and the V tile's scale ride
@@ -666,13 +672,17 @@ __device__ __forceinline__ void fetch_item_rows(const BatchRef& b, const ItemSpa
   const Geom* gp = reinterpret_cast<const Geom*>(b.table + b.off_geoms + static_cast<size_t>(c.r) * sizeof(Geom));
   if (kind == 2) {
     if (lane >= 8) { ptx::mbar_arrive(bar); return; }          // no means, no scale: the arrivals still count
-    const int mt = gp->mtiles;
-    const int head = in_req / mt, tile = in_req - head * mt;
-    const int row = tile * kQTile + half * 64 + w * 8 + lane;
-    if (row < gp->T && head < gp->Hq) {
+    // 64 consecutive PACKED rows of a kv head: row R is token R / group, head kvh * group + R % group;
+    // the group's heads of a token are neighbours in memory
+    const int pts = gp->ptiles, group = gp->Hq / gp->Hkv;
+    const int kvh = in_req / pts, pt = in_req - kvh * pts;
+    const int R = pt * kQTile + half * 64 + w * 8 + lane;
+    const int token = R / group;
+    if (token < gp->T) {
+      const int head = kvh * group + (R - token * group);
       ptx::mbar_expect_tx(bar, kD * 2);
       ptx::bulk_g2s(stage + static_cast<uint32_t>(w * 8 + lane) * (kD * 2),
-                    reinterpret_cast<const uint16_t*>(gp->q) + (static_cast<size_t>(row) * gp->Hq + head) * kD, kD * 2, bar);
+                    reinterpret_cast<const uint16_t*>(gp->q) + (static_cast<size_t>(token) * gp->Hq + head) * kD, kD * 2, bar);
     } else {
       ptx::mbar_arrive(bar);
     }
@@ -768,7 +778,7 @@ __global__ void __launch_bounds__(kThreads, 3) kv_transform_batch_kernel(BatchRe
       if (kind == 0) {
         transform_k_tile_staged<KV_DTYPE>(sg, in_req / sg.Hkv, in_req % sg.Hkv, stage, reinterpret_cast<const float*>(stage + kStageMeanOff));
       } else {
-        quantize_q_half_staged(sg, in_req / sg.mtiles, in_req % sg.mtiles, half, stage);
+        quantize_q_half_staged(sg, in_req / sg.ptiles, in_req % sg.ptiles, half, stage);
       }
     } else {
       uint4 raw[8];

@@ -82,21 +82,23 @@ def test_plan_writes_header_totals_and_a_longest_first_work_list(K):
     hdr = table[:64].view(np.int32)
     nt = [(n + 63) // 64 for _, n, _ in shapes]
     mt = [(t + 127) // 128 for t, _, _ in shapes]
-    assert hdr[1] == 3 and hdr[2] == sum(nt) * 4 and hdr[3] == sum(mt) * 24 and hdr[4] == sum(mt) * 24
+    # attention items: 128 packed (token, head) rows of one kv head's group of 6 q heads
+    pt = [(t * 6 + 127) // 128 for t, _, _ in shapes]               # 7, 1, 12
+    assert hdr[1] == 3 and hdr[2] == sum(nt) * 4 and hdr[3] == sum(pt) * 4 and hdr[4] == sum(pt) * 4
     stat = table[lay.table_off_stat_totals:lay.table_off_stat_totals + 5 * 4].view(np.int32)
     assert stat.tolist() == [0, nt[0] * 4, (nt[0] + nt[1]) * 4, sum(nt) * 4, sum(nt) * 4]
     qcta = table[lay.table_off_qcta_totals:lay.table_off_qcta_totals + 5 * 4].view(np.int32)
-    assert qcta.tolist() == [0, mt[0] * 24, (mt[0] + mt[1]) * 24, sum(mt) * 24, sum(mt) * 24]
+    assert qcta.tolist() == [0, pt[0] * 4, (pt[0] + pt[1]) * 4, sum(pt) * 4, sum(pt) * 4]
     items = table[lay.table_off_items:lay.table_off_items + hdr[4] * 8].view(np.int32).reshape(-1, 2)
-    # requests in order of attended pairs (2, 0, 1); inside a request deepest q tile first, heads together
-    assert items[:, 0].tolist() == [2] * 48 + [0] * 48 + [1] * 24
-    assert (items[:24, 1] & 0xFFFF).tolist() == [1] * 24 and (items[24:48, 1] & 0xFFFF).tolist() == [0] * 24
-    assert (items[:24, 1] >> 16).tolist() == list(range(24))
-    # every (request, head, tile) exactly once
+    # requests in order of attended pairs (2, 0, 1); inside a request deepest packed tile first, kv heads together
+    assert items[:, 0].tolist() == [2] * 48 + [0] * 28 + [1] * 4
+    assert (items[:4, 1] & 0xFFFF).tolist() == [11] * 4 and (items[44:48, 1] & 0xFFFF).tolist() == [0] * 4
+    assert (items[:8, 1] >> 16).tolist() == [0, 1, 2, 3, 0, 1, 2, 3]
+    # every (request, kv head, packed tile) exactly once
     assert len({(int(r), int(w)) for r, w in items}) == len(items)
     # planning again into the same buffer for fewer requests shrinks the counts (graph replay case)
     assert lib.akl_batch_plan(ctypes.byref(b), _reqs(K, shapes[:1]), 1, table.ctypes.data) == K.AKL_OK
-    assert table[:64].view(np.int32)[1] == 1 and table[:64].view(np.int32)[4] == 2 * 24
+    assert table[:64].view(np.int32)[1] == 1 and table[:64].view(np.int32)[4] == 7 * 4
 
 
 @pytest.mark.parametrize("shapes, over, batch_over, code", [
