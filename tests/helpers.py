@@ -8,8 +8,8 @@ import torch
 
 import akl_oracle as O
 
-#: measured parity figures, keyed "section/case/mode"; tests/conftest.py writes them to
-#: gpurun_out/parity_ledger.json when the session ends (the numbers quoted in the design notes)
+#: measured parity figures, keyed "section/case/mode"; tests/conftest.py writes them to a
+#: parity_ledger.json in the run's output folder when the session ends
 LEDGER: dict = {}
 
 
