@@ -53,7 +53,13 @@ def test_kv_split_ranges_are_tile_aligned_and_cover(pkg):
 
 
 # ------------------------------------------------------------------ two gloo ranks
-CASE = cases._case("split2", 96, 2500, 2404, 16, 4, "scattered", "outlier", 4301)
+CASES = {
+    # 96 rows divide over two ranks: the partial states themselves are the all-to-all send buffers
+    "even_rows": cases._case("split2", 96, 2500, 2404, 16, 4, "scattered", "outlier", 4301),
+    # 97 rows do not: the exchange pads them to 98
+    "odd_rows": cases._case("split2odd", 97, 2500, 2403, 16, 4, "scattered", "outlier", 4302),
+}
+CASE = CASES["even_rows"]
 
 
 class OraclePhases:
@@ -102,7 +108,8 @@ def _oracle_merge(parts_o, parts_l):
     return torch.from_numpy(o).to(torch.bfloat16), torch.from_numpy(l)
 
 
-def _rank_main(rank: int, world: int, port: int, result_path: str):
+def _rank_main(rank: int, world: int, port: int, result_path: str, case_key: str):
+    CASE = CASES[case_key]
     import sys
     import pathlib
 
@@ -152,11 +159,13 @@ def _rank_main(rank: int, world: int, port: int, result_path: str):
         dist.destroy_process_group()
 
 
-def test_kv_split_choreography_two_gloo_ranks(pkg, tmp_path):
+@pytest.mark.parametrize("case_key", ["even_rows", "odd_rows"])
+def test_kv_split_choreography_two_gloo_ranks(pkg, tmp_path, case_key):
+    CASE = CASES[case_key]
     world = 2
     port = _free_port()
     path = str(tmp_path / "res")
-    mp.spawn(_rank_main, args=(world, port, path), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, port, path, case_key), nprocs=world, join=True)
     parts = [torch.load(f"{path}.{r}") for r in range(world)]
 
     # single-process answer: request-wide statistics, per-split operator, float64 merge
