@@ -101,6 +101,27 @@ def test_plan_writes_header_totals_and_a_longest_first_work_list(K):
     assert table[:64].view(np.int32)[1] == 1 and table[:64].view(np.int32)[4] == 7 * 4
 
 
+@pytest.mark.parametrize("hq, hkv", [(16, 4), (32, 4), (8, 2), (4, 4)])
+def test_work_list_counts_packed_tiles_for_every_group_size(K, hq, hkv):
+    """An attention item is 128 packed (token, head) rows of one kv head's group of q heads, so a
+    request of T tokens has hkv * ceil(T * group / 128) of them, each exactly once, and the Q
+    quantisation totals count the same tiles."""
+    lib = K.load()
+    b, lay = _batch(K, _caps(K, hq=hq, hkv=hkv))
+    group = hq // hkv
+    shapes = [(1, 9, 8), (127, 127, 0), (129, 1000, 871), (300, 300, 0)]
+    table = np.zeros(lay.table_bytes, dtype=np.uint8)
+    assert lib.akl_batch_plan(ctypes.byref(b), _reqs(K, shapes), 4, table.ctypes.data) == K.AKL_OK
+    hdr = table[:64].view(np.int32)
+    pt = [(t * group + 127) // 128 for t, _, _ in shapes]
+    assert hdr[3] == sum(pt) * hkv and hdr[4] == sum(pt) * hkv
+    items = table[lay.table_off_items:lay.table_off_items + hdr[4] * 8].view(np.int32).reshape(-1, 2)
+    seen = {(int(r), int(w) >> 16, int(w) & 0xFFFF) for r, w in items}
+    assert seen == {(r, kvh, t) for r in range(4) for kvh in range(hkv) for t in range(pt[r])}
+    # never more tiles than one 128-row tile per q head would take
+    assert all(p <= group * ((t + 127) // 128) for p, (t, _, _) in zip(pt, shapes))
+
+
 @pytest.mark.parametrize("shapes, over, batch_over, code", [
     ([(64, 320, 257)], {}, {}, "AKL_ERR_INVALID"),                  # prefix > N - T
     ([(0, 320, 0)], {}, {}, "AKL_ERR_INVALID"),
